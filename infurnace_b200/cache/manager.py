@@ -13,7 +13,8 @@ with a window of w keys form another; calls with fixed-size state a third.  A ke
 group has a page pool and, for each request, a block table of its own, because its
 pages come and go by its own rule: a full-attention group holds a request's pages
 until the request ends, a window group gives a page back as soon as every key in it
-lies below the window of the request's next query.  Each cache entry (one per layer
+lies below the window of the request's next query, and a chunk group (a query sees the
+keys of its own chunk of positions only) as soon as the next query stands in a later chunk.  Each cache entry (one per layer
 call that stores) of a group has a tensor ``[pages, 2, kv_heads, page_size, head_dim]``
 (keys and values of one shape), or, for a need whose streams differ in shape (values narrower
 than keys, a latent beside a small rotated key), one tensor ``[pages, heads, page_size, width]``
@@ -58,9 +59,13 @@ class KVGroup:
 
     def first_needed_page(self, next_position: int) -> int:
         """Index of the first logical page that the query at ``next_position`` can read."""
-        if self.need.window is None:
-            return 0
-        return max(0, next_position - self.need.window + 1) // self.page_size
+        first = 0
+        if self.need.window is not None:
+            first = max(0, next_position - self.need.window + 1)
+        chunk = getattr(self.need, "chunk", None)
+        if chunk:
+            first = max(first, (next_position // chunk) * chunk)       # keys of earlier chunks are never read again
+        return first // self.page_size
 
 
 @dataclass
@@ -278,7 +283,7 @@ class CacheManager:
             if len(g.tables[rid]) < -(-nxt // self.page_size):
                 raise CacheError(f"request {rid!r} committed tokens for which it holds no pages")
         for g in self.kv_groups:
-            if g.need.window is None:
+            if g.need.window is None and not getattr(g.need, "chunk", None):
                 continue
             table = g.tables[rid]
             first = min(g.first_needed_page(nxt), len(table))

@@ -2,5 +2,7 @@
 from .specs import (  # noqa: F401
     TensorSpec, KVCacheNeed, StateNeed, RMSNormSpec, RotarySpec, AttentionSpec, GatedMLPSpec,
     PreNormBlockSpec, EmbeddingSpec, LMHeadSpec, LayerCall, ModelPlan,
+    ScalarRMSNormSpec, SinusoidEmbeddingSpec, DenseMLPSpec, GatedRecurrenceSpec, TalkingAttentionSpec, PostNormBlockSpec,
 )
 from .qwen3 import Qwen3Config  # noqa: F401
+from .kafunex import KafunexConfig  # noqa: F401

@@ -28,9 +28,12 @@ from typing import Mapping, Optional, Tuple
 @dataclass(frozen=True)
 class TensorSpec:
     """One tensor of a model folder.  ``kind`` is "float" (kept in the engine's weight
-    dtype, see weights/loader.py) or "int" (an integer table, kept as int32)."""
+    dtype, see weights/loader.py) or "int" (an integer table, kept as int32).  ``init``:
+    (mean, standard deviation) of the tensor in random-weights mode, where its shape alone
+    would give the wrong idea (a single number that is a norm weight, a lower bound in (0, 1))."""
     shape: Tuple[int, ...]
     kind: str = "float"
+    init: Optional[Tuple[float, float]] = None
 
 
 # --------------------------------------------------------------------------- cache needs
@@ -49,11 +52,14 @@ class KVCacheNeed:
     ``window`` None: every earlier key stays visible.  ``window`` w: a query at
     position p sees keys at positions p-w+1 .. p, and pages that lie wholly below
     that range are given back while the request still runs.  ``value_head_dim``: the
-    width of a value head where it differs from a key head's."""
+    width of a value head where it differs from a key head's.  ``chunk`` c: a query at
+    position p sees the keys of its own chunk only, positions (p // c) * c .. p, and the
+    pages of a chunk are given back once the request's next position lies in a later one."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
 
     @property
     def streams(self) -> Tuple[PagedStream, ...]:
@@ -62,7 +68,7 @@ class KVCacheNeed:
 
     @property
     def group_key(self):
-        return ("kv", self.streams, self.window)
+        return ("kv", self.streams, self.window) if self.chunk is None else ("kv", self.streams, self.window, ("chunk", self.chunk))
 
 
 @dataclass(frozen=True)
@@ -225,6 +231,163 @@ class LMHeadSpec:
         if self.tied:
             return {}
         return {self.weight: TensorSpec((self.vocab_size, self.hidden_size))}
+
+
+# --------------------------------------------------------------------------- parts of post-norm decoders
+@dataclass(frozen=True)
+class ScalarRMSNormSpec:
+    """y = x / sqrt(mean(x^2) + eps) * g with g a single number (a tensor of shape ())."""
+    eps: float
+    weight: str
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        return {self.weight: TensorSpec((), init=(1.0, 0.1))}
+
+
+@dataclass(frozen=True)
+class SinusoidEmbeddingSpec:
+    """x[t] = table[id_t] + e(position_t), e[2i] = sin(p * base^(-2i/width)), e[2i+1] = cos of the same angle."""
+    vocab_size: int
+    hidden_size: int
+    weight: str
+    base: float = 10000.0
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        return {self.weight: TensorSpec((self.vocab_size, self.hidden_size))}
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """x -> down(act(up(x))), no gate, no bias.  ``activation``: "relu2" (the square of relu), "silu",
+    "gelu_tanh"."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str
+    up_proj: str
+    down_proj: str
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        return {self.up_proj: TensorSpec((self.intermediate_size, self.hidden_size)),
+                self.down_proj: TensorSpec((self.hidden_size, self.intermediate_size))}
+
+    def cache_need(self):
+        return None
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceSpec:
+    """The HGRN2 mixer: linear attention whose forget gate also sets what is written.
+
+    Per head a float32 state S [dim, vdim], zero at the start of a sequence:
+    q = silu(Q h), f = lower + (1 - lower) * sigmoid(F h + bias), v = V h;
+    S <- diag(f) S + (1 - f) v^T;  o = S^T q;  each head's o is RMS-normalised over vdim with the
+    weight ``out_norm`` (shared by the heads) and the heads side by side go through ``o_proj``."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    value_head_dim: int
+    eps: float
+    q_proj: str
+    f_proj: str
+    f_bias: str
+    lower: str
+    v_proj: str
+    out_norm: str
+    o_proj: str
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        hd, hv = self.num_heads * self.head_dim, self.num_heads * self.value_head_dim
+        return {
+            self.q_proj: TensorSpec((hd, self.hidden_size)),
+            self.f_proj: TensorSpec((hd, self.hidden_size)),
+            self.f_bias: TensorSpec((hd,), init=(0.0, 0.5)),
+            self.lower: TensorSpec((hd,), init=(0.5, 0.1)),
+            self.v_proj: TensorSpec((hv, self.hidden_size)),
+            self.out_norm: TensorSpec((self.value_head_dim,)),
+            self.o_proj: TensorSpec((self.hidden_size, hv)),
+        }
+
+    def cache_need(self):
+        return StateNeed((self.num_heads, self.head_dim, self.value_head_dim))
+
+
+@dataclass(frozen=True)
+class TalkingAttentionSpec:
+    """Grouped-query softmax attention whose heads' scores are mixed before the softmax.
+
+    q = Q h, k = K h.  ``q_norm`` / ``k_norm``: RMSNorm of the WHOLE projection (one statistic per token
+    over all heads) with a weight of that length.  ``values_are_keys``: the values are k as projected,
+    before its norm, and there is no value projection.  No rotation; the position enters as a bias:
+    a[j] = scale * q_j . k - slope_j * (distance), slope_j = 2^(-slope_exponent * (j + 1) / heads)
+    (``slope_exponent`` None: no bias).  ``talk`` [heads, heads]: b[j] = sum_i talk[j, i] a[i]
+    (None: b = a).  ``chunk`` c: position p sees s <= p with s // c == p // c (None: every s <= p).
+    ``gate``: the heads side by side are multiplied by sigmoid(G h) before ``o_proj``."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    scale: float
+    eps: float
+    q_proj: str
+    k_proj: str
+    o_proj: str
+    v_proj: Optional[str] = None
+    q_norm: Optional[str] = None
+    k_norm: Optional[str] = None
+    talk: Optional[str] = None
+    gate: Optional[str] = None
+    chunk: Optional[int] = None
+    slope_exponent: Optional[float] = 8.0
+
+    @property
+    def values_are_keys(self) -> bool:
+        return self.v_proj is None
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        qw, kw = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        t = {self.q_proj: TensorSpec((qw, self.hidden_size)), self.k_proj: TensorSpec((kw, self.hidden_size)),
+             self.o_proj: TensorSpec((self.hidden_size, qw))}
+        if self.v_proj is not None:
+            t[self.v_proj] = TensorSpec((kw, self.hidden_size))
+        if self.q_norm is not None:
+            t[self.q_norm] = TensorSpec((qw,))
+        if self.k_norm is not None:
+            t[self.k_norm] = TensorSpec((kw,))
+        if self.talk is not None:
+            t[self.talk] = TensorSpec((self.num_heads, self.num_heads), init=(0.0, 0.35))
+        if self.gate is not None:
+            t[self.gate] = TensorSpec((qw, self.hidden_size))
+        return t
+
+    def cache_need(self):
+        return KVCacheNeed(self.num_kv_heads, self.head_dim, chunk=self.chunk)
+
+
+@dataclass(frozen=True)
+class PostNormBlockSpec:
+    """x += scale1 * norm1(mixer(x)); x += scale2 * norm2(ffn(x)).  The sublayers read x itself; the norm
+    is on the sublayer's result; ``mixer_scale`` / ``ffn_scale`` name per-feature vectors (layer scale).
+    ``ffn`` None: the block has no feed-forward (and neither its norm nor its scale)."""
+    hidden_size: int
+    mixer: object
+    mixer_norm: object
+    mixer_scale: str
+    ffn: Optional[object] = None
+    ffn_norm: Optional[object] = None
+    ffn_scale: Optional[str] = None
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        t = {}
+        for part in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm):
+            if part is not None:
+                t.update(part.tensors())
+        t[self.mixer_scale] = TensorSpec((self.hidden_size,))
+        if self.ffn is not None:
+            t[self.ffn_scale] = TensorSpec((self.hidden_size,))
+        return t
+
+    def cache_need(self):
+        return self.mixer.cache_need()
 
 
 # --------------------------------------------------------------------------- the order

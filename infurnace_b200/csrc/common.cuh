@@ -175,6 +175,24 @@ __device__ __forceinline__ void store_from_f32(void* p, int dtype, size_t i, flo
   if (dtype == IFB_F32) ((float*)p)[i] = v; else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
 }
 
+// A function of one number applied to each element of a product before it is stored (the `epilogue` argument of the
+// products carries it in the bits above the lowest four): 0 none, 1 relu(y)^2, 2 silu, 3 sigmoid, 4 gelu (tanh form).
+#define IFB_UNARY_NONE 0
+#define IFB_UNARY_RELU2 1
+#define IFB_UNARY_SILU 2
+#define IFB_UNARY_SIGMOID 3
+#define IFB_UNARY_GELU_TANH 4
+#define IFB_UNARY_LAST 4
+__device__ __forceinline__ float ifb_unary(float y, int kind) {
+  switch (kind) {
+    case IFB_UNARY_RELU2: { const float r = fmaxf(y, 0.f); return r * r; }
+    case IFB_UNARY_SILU: return y / (1.f + expf(-y));
+    case IFB_UNARY_SIGMOID: return 1.f / (1.f + expf(-y));
+    case IFB_UNARY_GELU_TANH: return 0.5f * y * (1.f + tanhf(0.7978845608028654f * (y + 0.044715f * y * y * y)));
+    default: return y;
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -1,0 +1,189 @@
+// The gated linear recurrence of an HGRN2 mixer, for prompts, portions of prompts and single decoded tokens alike.
+//
+// Per request and head a float32 state S [dim][vdim] lives in the request's state slot.  For each of the request's
+// tokens of this step, in order:
+//     q = silu(q_raw),  f = lower + (1 - lower) * sigmoid(f_raw + bias)                       (dim numbers each)
+//     S[i][c] = f[i] * S[i][c] + (1 - f[i]) * v[c]
+//     o[c]    = sum_i S[i][c] * q[i]
+//     out[c]  = o[c] / sqrt(mean_c(o^2) + eps) * norm_weight[c]
+// The columns c of S evolve independently, so a thread owns one column with its dim entries in registers; a block is
+// one (request, head) with a thread per column.  Tokens are staged in groups: the block loads q_raw, f_raw and v of a
+// group into shared memory and applies the activations once per number while doing so, every thread then walks the
+// group's tokens, and at the end of the group the head's outputs are normalised, a warp per token.  A head with more
+// columns than a block has threads (the more rows a thread keeps, the fewer threads a block may have) is split into
+// slabs of columns, a block each; the outputs then go to a float32 scratch and a second kernel normalises them.
+// Everything is float32; proj holds the projections as the product wrote them (float32).
+#include "common.cuh"
+#include <math.h>
+
+constexpr int GS_GROUP = 16;       // tokens staged at a time
+
+struct GatedScanArgs {
+  const float* proj;       // [tokens][ld]: q_raw at q_col, f_raw at f_col (heads * dim each), v at v_col (heads * vdim)
+  int ld, q_col, f_col, v_col;
+  const void* bias;        // [heads * dim]
+  const void* lower;       // [heads * dim]
+  const void* norm_w;      // [vdim], shared by the heads
+  int w_dtype;
+  float eps;
+  float* state;            // [slots][heads][dim][vdim]
+  const int* state_slots;  // [requests]
+  const int* cu_q;         // [requests + 1]
+  const int* seq_lens;     // [requests]; a request of length 0 is padding and is skipped
+  void* out;               // [tokens][heads * vdim], T
+  float* raw;              // [tokens][heads * vdim]: the outputs before the norm, when a head has several slabs (else null)
+  int heads, dim, vdim, slabs;
+};
+
+constexpr int gs_max_threads(int dmax) { return dmax <= 32 ? 512 : dmax <= 64 ? 256 : 128; }
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(gs_max_threads(DMAX), 1)
+gated_scan_kernel(GatedScanArgs a) {
+  extern __shared__ float sm[];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int r = blockIdx.y, h = blockIdx.x / a.slabs, c0 = (blockIdx.x % a.slabs) * blockDim.x, c = c0 + threadIdx.x;
+  const int dim = a.dim, vdim = a.vdim;
+  const int width = min((int)blockDim.x, vdim - c0);        // columns of this block
+  if (a.seq_lens[r] <= 0) return;
+  const int t0 = a.cu_q[r], t1 = a.cu_q[r + 1];
+  float* qs = sm;                              // [GROUP][DMAX]
+  float* fs = qs + GS_GROUP * DMAX;            // [GROUP][DMAX]
+  float* vs = fs + GS_GROUP * DMAX;            // [GROUP][threads]
+  float* os = vs + GS_GROUP * blockDim.x;      // [GROUP][threads]
+  const bool col = c < vdim;
+  float* sp = a.state + (((size_t)a.state_slots[r] * a.heads + h) * dim) * vdim + c;
+  float S[DMAX];
+#pragma unroll
+  for (int i = 0; i < DMAX; ++i) S[i] = (col && i < dim) ? sp[(size_t)i * vdim] : 0.f;
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int g0 = t0; g0 < t1; g0 += GS_GROUP) {
+    const int cnt = min(GS_GROUP, t1 - g0);
+    // rows dim .. DMAX-1 are padding: f = 1 keeps their (zero) entries, q = 0 keeps them out of the sums
+    for (int idx = threadIdx.x; idx < cnt * DMAX; idx += blockDim.x) {
+      const int t = idx / DMAX, i = idx % DMAX;
+      float qv = 0.f, fv = 1.f;
+      if (i < dim) {
+        const float* row = a.proj + (size_t)(g0 + t) * a.ld;
+        const float qr = row[a.q_col + h * dim + i];
+        qv = qr / (1.f + expf(-qr));
+        const float lo = load_as_f32(a.lower, a.w_dtype, h * dim + i);
+        const float z = row[a.f_col + h * dim + i] + load_as_f32(a.bias, a.w_dtype, h * dim + i);
+        fv = lo + (1.f - lo) * (1.f / (1.f + expf(-z)));
+      }
+      qs[idx] = qv;
+      fs[idx] = fv;
+    }
+    for (int idx = threadIdx.x; idx < cnt * width; idx += blockDim.x) {
+      const int t = idx / width, e = idx % width;
+      vs[t * blockDim.x + e] = a.proj[(size_t)(g0 + t) * a.ld + a.v_col + h * vdim + c0 + e];
+    }
+    __syncthreads();
+    if (col) {
+      for (int t = 0; t < cnt; ++t) {
+        const float v = vs[t * blockDim.x + threadIdx.x];
+        const float4* q = reinterpret_cast<const float4*>(qs + t * DMAX);
+        const float4* f = reinterpret_cast<const float4*>(fs + t * DMAX);
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < DMAX / 4; ++i) {
+          const float4 fi = f[i], qi = q[i];
+          S[4 * i] = fmaf(fi.x, S[4 * i], (1.f - fi.x) * v);             o0 = fmaf(S[4 * i], qi.x, o0);
+          S[4 * i + 1] = fmaf(fi.y, S[4 * i + 1], (1.f - fi.y) * v);     o1 = fmaf(S[4 * i + 1], qi.y, o1);
+          S[4 * i + 2] = fmaf(fi.z, S[4 * i + 2], (1.f - fi.z) * v);     o2 = fmaf(S[4 * i + 2], qi.z, o2);
+          S[4 * i + 3] = fmaf(fi.w, S[4 * i + 3], (1.f - fi.w) * v);     o3 = fmaf(S[4 * i + 3], qi.w, o3);
+        }
+        os[t * blockDim.x + threadIdx.x] = (o0 + o1) + (o2 + o3);
+      }
+    }
+    __syncthreads();
+    for (int t = warp; t < cnt; t += warps) {           // the head's norm, a warp per token
+      const float* o = os + t * blockDim.x;
+      if (a.raw) {                                      // the head has other slabs: its norm is the second kernel's
+        float* dst = a.raw + ((size_t)(g0 + t) * a.heads + h) * vdim + c0;
+        for (int e = lane; e < width; e += 32) dst[e] = o[e];
+        continue;
+      }
+      float ss = 0.f;
+      for (int e = lane; e < vdim; e += 32) ss += o[e] * o[e];
+      const float rn = 1.f / sqrtf(warp_sum(ss) / (float)vdim + a.eps);
+      T* dst = (T*)a.out + ((size_t)(g0 + t) * a.heads + h) * vdim;
+      for (int e = lane; e < vdim; e += 32) dst[e] = from_f32<T>(o[e] * rn * load_as_f32(a.norm_w, a.w_dtype, e));
+    }
+    __syncthreads();
+  }
+  if (col) {
+#pragma unroll
+    for (int i = 0; i < DMAX; ++i)
+      if (i < dim) sp[(size_t)i * vdim] = S[i];
+  }
+}
+
+// out[t, h, :] = raw[t, h, :] / sqrt(mean(raw[t, h, :]^2) + eps) * w, a warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_kernel(const float* __restrict__ raw, const void* __restrict__ w, int w_dtype, float eps, T* __restrict__ out,
+                 long long items, int vdim) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const float* o = raw + item * vdim;
+  float ss = 0.f;
+  for (int e = lane; e < vdim; e += 32) ss += o[e] * o[e];
+  const float rn = 1.f / sqrtf(warp_sum(ss) / (float)vdim + eps);
+  for (int e = lane; e < vdim; e += 32) out[item * vdim + e] = from_f32<T>(o[e] * rn * load_as_f32(w, w_dtype, e));
+}
+
+static int gs_block_threads(int dim, int vdim) {
+  const int cap = gs_max_threads(dim <= 16 ? 16 : dim <= 32 ? 32 : dim <= 64 ? 64 : 128);
+  return min(cap, ((vdim + 31) / 32) * 32);
+}
+
+template <typename T>
+static int gs_launch(GatedScanArgs a, int requests, int tokens, cudaStream_t s) {
+  const int threads = gs_block_threads(a.dim, a.vdim);
+  a.slabs = (a.vdim + threads - 1) / threads;
+  if (a.slabs > 1 && !a.raw) return IFB_ERR_ARG;
+  if (a.slabs == 1) a.raw = nullptr;
+  dim3 grid(a.heads * a.slabs, requests);
+  int st = IFB_ERR_SIZE;
+  bool done = false;
+#define GS_CASE(D)                                                                     \
+  if (!done && a.dim <= D) {                                                           \
+    const size_t smem = (size_t)GS_GROUP * (2 * D + 2 * threads) * sizeof(float);      \
+    done = true;                                                                       \
+    IFB_ALLOW_SMEM((gated_scan_kernel<T, D>), smem);                                   \
+    st = ifb_launch(gated_scan_kernel<T, D>, grid, dim3(threads), smem, s, a);         \
+  }
+  GS_CASE(16) GS_CASE(32) GS_CASE(64) GS_CASE(128)
+#undef GS_CASE
+  if (st != IFB_OK || a.slabs == 1) return st;
+  const long long items = (long long)tokens * a.heads;
+  return ifb_launch(head_norm_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, (const float*)a.raw, a.norm_w,
+                    a.w_dtype, a.eps, (T*)a.out, items, a.vdim);
+}
+
+// Slabs of columns that a head of these sizes is split into; with more than one the caller gives `raw`.
+IFB_EXPORT int ifb_gated_scan_slabs(int dim, int vdim) {
+  const int threads = gs_block_threads(dim, vdim);
+  return (vdim + threads - 1) / threads;
+}
+
+// dim up to 128, any vdim.  bias, lower and norm_w share one dtype.  raw: float32 [tokens][heads * vdim] scratch, needed
+// when ifb_gated_scan_slabs(dim, vdim) > 1.
+IFB_EXPORT int ifb_gated_scan(const float* proj, int ld, int q_col, int f_col, int v_col, const void* bias, const void* lower,
+                              const void* norm_w, int w_dtype, float eps, float* state, const int* state_slots, const int* cu_q,
+                              const int* seq_lens, void* out, int out_dtype, float* raw, int requests, int tokens, int heads,
+                              int dim, int vdim, cudaStream_t stream) {
+  if (requests <= 0 || tokens <= 0) return IFB_OK;
+  if (heads < 1 || dim < 1 || vdim < 1 || dim > 128 || requests > 65535) return IFB_ERR_SIZE;
+  if (w_dtype != IFB_F32 && w_dtype != IFB_BF16) return IFB_ERR_DTYPE;
+  GatedScanArgs a{proj, ld, q_col, f_col, v_col, bias, lower, norm_w, w_dtype, eps, state, state_slots, cu_q, seq_lens, out,
+                  raw, heads, dim, vdim, 1};
+  if (out_dtype == IFB_F32) return gs_launch<float>(a, requests, tokens, stream);
+  if (out_dtype == IFB_BF16) return gs_launch<__nv_bfloat16>(a, requests, tokens, stream);
+  return IFB_ERR_DTYPE;
+}

@@ -42,6 +42,7 @@ struct GvRowScale {        // consumer side: null `partials` = none
   const float* partials;   // [parts][n_rows] partial sums of squares
   int parts;
   float eps, inv_width;    // r = rsqrt(sum * inv_width + eps)
+  int unary;               // plain epilogue only: the function of common.cuh applied to every element (0: none)
 };
 struct GvResidual {        // producer side, epilogue 2
   float* x;                // [n_rows][o_out] float32 residual stream, updated in place: v = x + y
@@ -324,7 +325,7 @@ linear_gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TO* _
       sq += __shfl_xor_sync(0xffffffffu, sq, 1);
       if (m == 0 && tok < n_rows) res.partials[(size_t)blockIdx.x * n_rows + tok] = sq;
     } else if (valid) {
-      out[(size_t)tok * o_out + o] = from_f32<TO>(r);
+      out[(size_t)tok * o_out + o] = from_f32<TO>((EPI == 0 && rs.unary) ? ifb_unary(r, rs.unary) : r);
     }
   }
   if (EPI == 3) {
@@ -500,11 +501,13 @@ IFB_EXPORT int ifb_linear_gemv(const void* x, const void* w, void* out, int out_
   if (n_rows <= 0 || out_features <= 0) return IFB_OK;
   if (k_dim < 8 || k_dim % 8) return IFB_ERR_SIZE;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return IFB_ERR_ALIGN;
-  if (epilogue != 0 && epilogue != 1) return IFB_ERR_ARG;
+  const int unary = epilogue >> 4;
+  epilogue &= 15;
+  if (epilogue > 1 || unary < 0 || unary > IFB_UNARY_LAST || (epilogue && unary)) return IFB_ERR_ARG;
   if (scale_partials && (scale_parts < 1 || scale_width < 1)) return IFB_ERR_ARG;
   const int nb = gv_blocks_of_8(n_rows);
   if ((n_rows + nb * 8 - 1) / (nb * 8) > 65535) return IFB_ERR_SIZE;
-  GvRowScale rs{scale_partials, scale_parts, scale_eps, scale_partials ? 1.f / (float)scale_width : 0.f};
+  GvRowScale rs{scale_partials, scale_parts, scale_eps, scale_partials ? 1.f / (float)scale_width : 0.f, unary};
   GvResidual res{nullptr, nullptr, 0, nullptr};
   if (out_dtype == IFB_BF16)
     return epilogue ? gv_by_k<1, bf16>(nb, x, w, out, n_rows, out_features, k_dim, rs, res, stream)

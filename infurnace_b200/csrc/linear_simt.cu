@@ -10,12 +10,12 @@
 #define TILE_O 64
 #define TILE_K 16
 
-// EPI 0: out = y.  EPI 1 (silu_gate): w has 2*o_out rows, gate rows first;
+// EPI 0: out = unary(y) (common.cuh: ifb_unary; 0 = y itself).  EPI 1 (silu_gate): w has 2*o_out rows, gate rows first;
 // out[n, o] = silu(y[n, o]) * y[n, o_out + o].
 template <typename TX, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 linear_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out, int n_rows, int o_out,
-                   int k_dim) {
+                   int k_dim, int unary) {
   __shared__ float xs[TILE_K][TILE_N + 1];
   __shared__ float ws[EPI ? 2 : 1][TILE_K][TILE_O + 1];
   ifb_pdl_wait();
@@ -77,6 +77,7 @@ linear_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __res
       if (o >= o_out) continue;
       float y = acc[0][i][j];
       if (EPI) { const float g = y; y = g / (1.f + expf(-g)) * acc[EPI ? 1 : 0][i][j]; }
+      else if (unary) y = ifb_unary(y, unary);
       out[(size_t)n * o_out + o] = from_f32<TO>(y);
     }
   }
@@ -85,17 +86,19 @@ linear_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __res
 template <typename TX, typename TW, typename TO>
 static int launch(const void* x, const void* w, void* out, int n, int o, int k, int epi, cudaStream_t s) {
   dim3 grid((o + TILE_O - 1) / TILE_O, (n + TILE_N - 1) / TILE_N);
-  if (epi == 0)
-    return ifb_launch(linear_simt_kernel<TX, TW, TO, 0>, grid, dim3(256), 0, s, (const TX*)x, (const TW*)w, (TO*)out, n, o, k);
-  return ifb_launch(linear_simt_kernel<TX, TW, TO, 1>, grid, dim3(256), 0, s, (const TX*)x, (const TW*)w, (TO*)out, n, o, k);
+  const int unary = epi >> 4;
+  if ((epi & 15) == 0)
+    return ifb_launch(linear_simt_kernel<TX, TW, TO, 0>, grid, dim3(256), 0, s, (const TX*)x, (const TW*)w, (TO*)out, n, o, k, unary);
+  return ifb_launch(linear_simt_kernel<TX, TW, TO, 1>, grid, dim3(256), 0, s, (const TX*)x, (const TW*)w, (TO*)out, n, o, k, 0);
 }
 
-// out_features is the width of `out` (for the silu_gate epilogue, half of w's rows).
+// out_features is the width of `out` (for the silu_gate epilogue, half of w's rows).  epilogue: 0 plain, 1 silu_gate,
+// 16 * u: plain with the unary function u of common.cuh applied to every element.
 IFB_EXPORT int ifb_linear_simt(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype,
                                int n_rows, int out_features, int k_dim, int epilogue, cudaStream_t stream) {
   if (n_rows <= 0 || out_features <= 0) return IFB_OK;
   if (k_dim < 1) return IFB_ERR_SIZE;
-  if (epilogue != 0 && epilogue != 1) return IFB_ERR_ARG;
+  if ((epilogue & 15) > 1 || (epilogue >> 4) > IFB_UNARY_LAST || ((epilogue & 15) && (epilogue >> 4)) || epilogue < 0) return IFB_ERR_ARG;
   if ((n_rows + TILE_N - 1) / TILE_N > 65535) return IFB_ERR_SIZE;
   typedef __nv_bfloat16 bf;
   const int key = x_dtype * 4 + w_dtype * 2 + out_dtype;

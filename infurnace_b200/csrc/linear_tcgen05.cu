@@ -156,6 +156,7 @@ struct TcFold {
   const void* res_g;          // [o_out] norm weight
   int res_g_dtype;
   float* res_partials;        // [parts][n_rows], written; what a part covers depends on the launch (tc_fold_parts)
+  int unary;                  // plain epilogue without res_x: the function of common.cuh applied to every element (0: none)
   // The product is the fused q | k | v projection of an attention layer with heads of 128, in the shared-k form, whose
   // tile of 128 features is one head: the sum over the cluster finishes what follows the projection (RMSNorm over the q
   // and k heads, rotation in the half-split pairing, q to its row, k and v to the token's place in the pages).
@@ -368,6 +369,10 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]) * rfac;
+            if (fold.unary) {                                    // warp-uniform
+#pragma unroll
+              for (int j = 0; j < 32; ++j) y[j] = ifb_unary(y[j], fold.unary);
+            }
           }
           if (!EPI && fold.res_x) ss += tc_residual_chunk(fold, y, row0 + lane, n_rows, n0 + c0, o_out);
           if (vec) {
@@ -440,6 +445,10 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         acc.w = acc.w * fast_rcp(1.f + fast_exp2(-1.4426950408889634f * acc.w)) * up.w;
       }
       TO* dst = out + (size_t)(m0 + r) * o_out + n0 + c;
+      if (!EPI && fold.unary) {
+        acc.x = ifb_unary(acc.x, fold.unary); acc.y = ifb_unary(acc.y, fold.unary);
+        acc.z = ifb_unary(acc.z, fold.unary); acc.w = ifb_unary(acc.w, fold.unary);
+      }
       if (!EPI && fold.res_x) {
         // a warp holds one row of the tile: v = x + y, x <- v, the output becomes v * g, the warp's sum of v^2 one part
         float* xr = fold.res_x + (size_t)(m0 + r) * o_out + n0 + c;
@@ -691,6 +700,10 @@ linear_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap tmap_x, con
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(v[j]) * rfac;
+            if (fold.unary) {                                    // warp-uniform
+#pragma unroll
+              for (int j = 0; j < 32; ++j) y[j] = ifb_unary(y[j], fold.unary);
+            }
           }
           if (vec) {
             unsigned char* dst = buf + lane * PITCH + (c0 - p0) * (int)sizeof(TO);
@@ -842,6 +855,7 @@ static int tc_launch(const void* x, const void* w, void* out, int n, int o, int 
   return tc_launch_cfg<Narrow, TO>(x, w, out, n, o, k, err, s, fold);
 }
 
+// epilogue: 0 plain, 1 silu_gate, 16 * u: plain with the unary function u of common.cuh applied to every element.
 // x [n_rows, k] and w [out_features (x2 for the silu_gate epilogue), k] bfloat16, 16-byte aligned, k a multiple of 8;
 // out bfloat16 or float32.  `err` points to a device int that stays 0 unless a bounded wait gave up.  shape: 0 lets the
 // library choose, 1-3 force the one-tile-per-CTA kernel narrow, deep or wide, 4 and 5 the persistent kernel with tiles
@@ -858,7 +872,9 @@ IFB_EXPORT int ifb_linear_tcgen05_ex(const void* x, const void* w, void* out, in
   if (n_rows <= 0 || out_features <= 0) return IFB_OK;
   if (k_dim < 8 || k_dim % 8) return IFB_ERR_SIZE;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return IFB_ERR_ALIGN;
-  if (epilogue != 0 && epilogue != 1) return IFB_ERR_ARG;
+  const int unary = epilogue >> 4;
+  epilogue &= 15;
+  if (epilogue > 1 || unary < 0 || unary > IFB_UNARY_LAST || (unary && (epilogue || res_x))) return IFB_ERR_ARG;
   if (shape < 0 || shape > 5 || splits < 0 || splits > 8) return IFB_ERR_ARG;
   if (scale_partials && (scale_parts < 1 || scale_width < 1)) return IFB_ERR_ARG;
   if (res_x && (!res_g || !res_partials || ((uintptr_t)res_x & 15))) return IFB_ERR_ARG;
@@ -866,6 +882,7 @@ IFB_EXPORT int ifb_linear_tcgen05_ex(const void* x, const void* w, void* out, in
   fold.rs_partials = scale_partials; fold.rs_parts = scale_parts; fold.rs_eps = scale_eps;
   fold.rs_inv_width = scale_partials ? 1.f / (float)scale_width : 0.f;
   fold.res_x = res_x; fold.res_g = res_g; fold.res_g_dtype = res_g_dtype; fold.res_partials = res_partials;
+  fold.unary = unary;
   if (out_dtype == IFB_BF16)
     return epilogue ? tc_launch<1, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream)
                     : tc_launch<0, bf16>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream);

@@ -35,6 +35,8 @@ LIBRARIES: Dict[str, tuple] = {
     # the few-rows product with its scratch inside the library, for callers that must not allocate
     "linear_skinny_static": (["linear_skinny_static.cu"], []),
     "attention_tc": (["attention_tc.cu"], []),            # head size 128
+    # post-norm sublayers (embedding with a position vector, residual update), the gated recurrence, talking attention
+    "mixers": (["sublayer.cu", "gated_scan.cu", "attention_talk.cu"], []),
     # compiled once per head size: defines={"HEAD_DIM": d}
     "attention_mma": (["attention_mma.cu"], []),
 }
@@ -192,7 +194,8 @@ def load_library(name: str, defines: Optional[Dict[str, object]] = None, progres
 def build_all(progress=None) -> List[str]:
     """Compile every library (used by the build check; needs no GPU)."""
     from concurrent.futures import ThreadPoolExecutor
-    jobs = [("core", None), ("linear_tcgen05", None), ("linear_skinny_static", None), ("attention_tc", None)] + DEFAULT_VARIANTS
+    jobs = [("core", None), ("linear_tcgen05", None), ("linear_skinny_static", None), ("attention_tc", None),
+            ("mixers", None)] + DEFAULT_VARIANTS
     with ThreadPoolExecutor(max_workers=4) as pool:
         built = list(pool.map(lambda j: compile_library(j[0], j[1], progress), jobs))
     # objects of older sources are never loaded (their names carry another hash); take them out of the folder

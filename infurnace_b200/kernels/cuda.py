@@ -17,6 +17,9 @@ from ..errors import KernelError
 from .build import load_library
 
 F32, BF16 = 0, 1
+# the `epilogue` argument of the products: 0 plain, 1 silu_gate (w holds gate rows, then up rows), 16 * u: plain with the
+# unary function u applied to every element (csrc/common.cuh: ifb_unary)
+EPILOGUES = {"none": 0, "silu_gate": 1, "relu2": 16, "silu": 32, "sigmoid": 48, "gelu_tanh": 64}
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 _ERRORS = {1: "a dtype (or combination of dtypes) has no kernel", 2: "a size is outside what the kernel takes",
            3: "an address or row length breaks the kernel's alignment rule", 4: "arguments contradict each other"}
@@ -102,6 +105,7 @@ class CudaKernels:
         # up to here norms are folded into products (the kernels take 64 rows; beyond 32 the separate norm measured faster)
         self.fold_max_rows = int(os.environ.get("INFURNACE_FOLD_MAX_ROWS", "32"))
         self.split_min_keys = int(os.environ.get("INFURNACE_SPLIT_MIN_KEYS", "256"))   # fewest keys a split of a context gets
+        self._mix = None               # the library of post-norm sublayers, the gated recurrence and talking attention
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
         # device int: non-zero after a kernel recorded a fault it contained (a bounded barrier wait that gave up, a
         # token id outside the vocabulary); read by check_device_errors
@@ -189,17 +193,22 @@ class CudaKernels:
 
     # ------------------------------------------------------------------ matrix products
     def linear(self, x, w, out, epilogue="none", row_scale=None):
-        """out = x w^T with the epilogue.  ``row_scale`` (partials, parts, eps, width), from
+        """out = x w^T with the epilogue (a key of ``EPILOGUES``).  ``row_scale`` (partials, parts, eps, width), from
         :meth:`linear_residual_norm`, multiplies row n by rsqrt(sum_p partials[p, n] / width + eps)
         before the epilogue; only where :meth:`can_fold_norm` says so."""
         _dense(x, "x"), _dense(w, "w"), _dense(out, "out")
         n, k = x.shape
         o = out.shape[1]
-        epi = {"none": 0, "silu_gate": 1}[epilogue]
-        if w.shape[1] != k or out.shape[0] != n or w.shape[0] != (2 * o if epi else o):
+        try:
+            epi = EPILOGUES[epilogue]
+        except KeyError:
+            raise KernelError(f"linear: unknown epilogue {epilogue!r}; known: {', '.join(EPILOGUES)}") from None
+        gated = epi == 1
+        route = "silu_gate" if gated else "none"          # a unary function changes nothing in the choice of kernel
+        if w.shape[1] != k or out.shape[0] != n or w.shape[0] != (2 * o if gated else o):
             raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not match")
         if row_scale is not None:
-            if not self.can_fold_norm(n, x.dtype, w, epilogue) or out.dtype not in (torch.bfloat16, torch.float32):
+            if not self.can_fold_norm(n, x.dtype, w, route) or out.dtype not in (torch.bfloat16, torch.float32):
                 raise KernelError("linear: a row scale is taken only by the bfloat16 kernels (see can_fold_norm)")
             partials, parts = row_scale[0], row_scale[1]
             _dense(partials, "row_scale partials", torch.float32)
@@ -207,8 +216,8 @@ class CudaKernels:
                 raise KernelError("linear: row_scale partials must be [parts, rows]")
         if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 \
                 and out.dtype in (torch.bfloat16, torch.float32):
-            if self._on_tcgen05(n, w, epilogue):
-                return self._linear_tcgen05(x, w, out, n, o, k, epi, splits=self.tcgen05_splits(n, o, k, epi),
+            if self._on_tcgen05(n, w, route):
+                return self._linear_tcgen05(x, w, out, n, o, k, epi, splits=self.tcgen05_splits(n, o, k, gated),
                                             row_scale=row_scale)
             return self._linear_gemv(x, w, out, n, o, k, epi, row_scale)
         self.launches += 1
@@ -628,6 +637,155 @@ class CudaKernels:
             self._dev_err.data_ptr(), n, r, num_heads, num_kv_heads, head_dim, kv_pages.shape[3], float(scale), int(window),
             int(max_q_len), int(num_splits), 1, 0 if only_small else 1, 1 if self.attention_tma else 0, self._stream()),
             "paged_attention")
+
+    # ------------------------------------------------------------------ post-norm sublayers, recurrence, talking attention
+    def _mix_lib(self):
+        if self._mix is None:
+            m = self._mix = load_library("mixers", progress=self._progress)
+            m.ifb_embed_sinusoid.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                             c_int, c_void_p, c_void_p]
+            m.ifb_residual_postnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int,
+                                                c_int, c_void_p]
+            m.ifb_cast_rows.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p]
+            m.ifb_wide_norm_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float,
+                                              c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+            m.ifb_gated_scan_slabs.argtypes = [c_int, c_int]
+            m.ifb_gated_scan.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                         c_int, c_int, c_void_p]
+            m.ifb_attention_talk.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                             c_float, c_float, c_void_p]
+        return self._mix
+
+    def embed_sinusoid(self, table, ids, positions, inv_freq, out, half=None):
+        """out[n] = table[ids[n]] + e(positions[n]) in float32, e[2i] = sin(p * inv_freq[i]), e[2i+1] = cos of the
+        same angle (inv_freq float64).  ``half``: the same rows in bfloat16, for the products that read them."""
+        _dense(table, "table"), _dense(ids, "ids", torch.int32), _dense(positions, "positions", torch.int32)
+        _dense(inv_freq, "inv_freq", torch.float64), _dense(out, "out", torch.float32)
+        n, hidden = out.shape
+        if table.shape[1] != hidden or ids.numel() != n or positions.numel() != n or inv_freq.numel() != (hidden + 1) // 2:
+            raise KernelError("embed_sinusoid: sizes of table, ids, positions, inv_freq and out do not match")
+        if half is not None and (_dense(half, "half", torch.bfloat16).shape != out.shape):
+            raise KernelError("embed_sinusoid: half has the shape of out")
+        self.launches += 1
+        self._err_armed = True
+        _check(self._mix_lib().ifb_embed_sinusoid(table.data_ptr(), _code(table), ids.data_ptr(), positions.data_ptr(),
+                                                  inv_freq.data_ptr(), out.data_ptr(), _ptr(half), n, hidden, table.shape[0],
+                                                  self._dev_err.data_ptr(), self._stream()), "embed_sinusoid")
+
+    def residual_postnorm(self, x, y, g, scale, eps, half=None):
+        """x += y / sqrt(mean(y^2) + eps) * g * scale, row by row in float32 (g: one number, scale: per feature).
+        ``half``: the updated rows in bfloat16."""
+        _dense(x, "x", torch.float32), _dense(y, "y", torch.float32), _dense(g, "g"), _dense(scale, "scale")
+        n, hidden = x.shape
+        if y.shape != x.shape or g.numel() != 1 or scale.numel() != hidden:
+            raise KernelError("residual_postnorm: sizes of x, y, g and scale do not match")
+        if half is not None and (_dense(half, "half", torch.bfloat16).shape != x.shape):
+            raise KernelError("residual_postnorm: half has the shape of x")
+        self.launches += 1
+        _check(self._mix_lib().ifb_residual_postnorm(x.data_ptr(), y.data_ptr(), g.data_ptr(), _code(g), scale.data_ptr(),
+                                                     _code(scale), float(eps), _ptr(half), n, hidden, self._stream()),
+               "residual_postnorm")
+
+    def cast_rows(self, x, out):
+        """out = x rounded to bfloat16 (x float32, same shape)."""
+        _dense(x, "x", torch.float32), _dense(out, "out", torch.bfloat16)
+        if out.shape != x.shape:
+            raise KernelError("cast_rows: out has the shape of x")
+        self.launches += 1
+        _check(self._mix_lib().ifb_cast_rows(x.data_ptr(), out.data_ptr(), x.numel(), self._stream()), "cast_rows")
+
+    def wide_norm_store(self, proj, q_width, k_width, v_col, head_dim, q_weight, k_weight, eps, q_out, slot_mapping, kv_pages):
+        """proj [n, >= q_width + k_width] float32 holds q then k of every token.  q_out = RMSNorm of the whole q
+        (one statistic per token) times q_weight; the key page gets the same of k; the value page gets k as
+        projected (``v_col`` < 0) or proj[:, v_col : v_col + k_width].  A weight of None: no norm."""
+        _dense(proj, "proj", torch.float32), _dense(q_out, "q_out")
+        n, ld = proj.shape
+        wd = F32
+        for wt, width in ((q_weight, q_width), (k_weight, k_width)):
+            if wt is not None:
+                _dense(wt, "norm weight")
+                if wt.numel() != width:
+                    raise KernelError("wide_norm_store: a norm weight has the length of its whole projection")
+                wd = _code(wt)
+        if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+            raise KernelError("wide_norm_store: q and k norm weights differ in dtype")
+        if q_out.shape != (n, q_width) or ld < q_width + k_width or (v_col >= 0 and ld < v_col + k_width):
+            raise KernelError("wide_norm_store: sizes of proj and q_out do not match the widths")
+        page_size = 1
+        if slot_mapping is not None:
+            _dense(slot_mapping, "slot_mapping", torch.int32), _dense(kv_pages, "kv_pages", q_out.dtype)
+            if kv_pages.dim() != 5 or kv_pages.shape[1] != 2 or kv_pages.shape[2] * kv_pages.shape[4] != k_width \
+                    or kv_pages.shape[4] != head_dim or slot_mapping.numel() != n:
+                raise KernelError("wide_norm_store: kv_pages is not [pages, 2, kv_heads, page_size, head_dim]")
+            page_size = kv_pages.shape[3]
+        self.launches += 1
+        _check(self._mix_lib().ifb_wide_norm_store(
+            proj.data_ptr(), ld, q_width, k_width, int(v_col), head_dim, _ptr(q_weight), _ptr(k_weight), wd, float(eps),
+            q_out.data_ptr(), _code(q_out), _ptr(slot_mapping), _ptr(kv_pages) if slot_mapping is not None else 0, page_size,
+            n, self._stream()), "wide_norm_store")
+
+    def gated_scan_slabs(self, dim, vdim):
+        """Column slabs a head of the gated recurrence is split into; with more than one, ``gated_scan`` needs ``raw``."""
+        return int(self._mix_lib().ifb_gated_scan_slabs(int(dim), int(vdim)))
+
+    def gated_scan(self, proj, q_col, f_col, v_col, bias, lower, norm_weight, eps, state, state_slots, cu_q, seq_lens, out,
+                   heads, dim, vdim, raw=None):
+        """The gated linear recurrence over this step's tokens of every request (csrc/gated_scan.cu): proj [n, ld]
+        float32 holds q_raw, f_raw (heads * dim each) and v (heads * vdim) at the given columns; state
+        [slots, heads, dim, vdim] float32 is read and written at each request's slot; out [n, heads * vdim] gets the
+        normalised outputs.  A request with seq_lens 0 is padding: its state is left alone."""
+        _dense(proj, "proj", torch.float32), _dense(state, "state", torch.float32), _dense(out, "out")
+        _dense(state_slots, "state_slots", torch.int32), _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
+        n, ld = proj.shape
+        r = seq_lens.numel()
+        hd, hv = heads * dim, heads * vdim
+        for t, size, name in ((bias, hd, "bias"), (lower, hd, "lower"), (norm_weight, vdim, "norm_weight")):
+            _dense(t, name)
+            if t.numel() != size or t.dtype != bias.dtype:
+                raise KernelError(f"gated_scan: {name} has the wrong length or a dtype of its own")
+        if state.shape[1:] != (heads, dim, vdim) or out.shape != (n, hv) or cu_q.numel() != r + 1 or state_slots.numel() < r \
+                or max(q_col, f_col) + hd > ld or v_col + hv > ld:
+            raise KernelError("gated_scan: sizes of proj, state, out and the request arrays do not match")
+        if raw is not None and (_dense(raw, "raw", torch.float32).shape != (n, hv)):
+            raise KernelError("gated_scan: raw is float32 [tokens, heads * vdim]")
+        self.launches += 1 if raw is None or self.gated_scan_slabs(dim, vdim) == 1 else 2
+        _check(self._mix_lib().ifb_gated_scan(
+            proj.data_ptr(), ld, int(q_col), int(f_col), int(v_col), bias.data_ptr(), lower.data_ptr(), norm_weight.data_ptr(),
+            _code(bias), float(eps), state.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(),
+            out.data_ptr(), _code(out), _ptr(raw), r, n, heads, dim, vdim, self._stream()), "gated_scan")
+
+    def attention_talk(self, q, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
+                       chunk=0, slope_exponent=0.0, talk=None, gate=None, gate_col=0, max_q_len=0):
+        """Attention over the pages with the heads' scores mixed before the softmax (csrc/attention_talk.cu).
+        q [n, heads * head_dim]: the queries, already normalised.  ``chunk`` 0: every earlier key is visible.
+        ``slope_exponent`` 0: no distance bias.  ``talk`` [heads, heads] or None.  ``gate``: a float32 matrix whose
+        columns gate_col .. gate_col + heads * head_dim hold the gate before its sigmoid, or None."""
+        _dense(q, "q"), _dense(kv_pages, "kv_pages", q.dtype), _dense(out, "out", q.dtype)
+        _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
+        if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
+            raise KernelError("attention_talk: block_tables must be int32 with unit stride along pages")
+        n, r = q.shape[0], seq_lens.numel()
+        width = num_heads * head_dim
+        if q.shape != (n, width) or out.shape != (n, width) or cu_q.numel() != r + 1 or block_tables.shape[0] < r:
+            raise KernelError("attention_talk: sizes of q, out, cu_q, seq_lens and block_tables do not match")
+        if kv_pages.dim() != 5 or kv_pages.shape[1] != 2 or kv_pages.shape[2] != num_kv_heads or kv_pages.shape[4] != head_dim:
+            raise KernelError("attention_talk: kv_pages is not [pages, 2, kv_heads, page_size, head_dim]")
+        if talk is not None and _dense(talk, "talk").shape != (num_heads, num_heads):
+            raise KernelError("attention_talk: talk is [heads, heads]")
+        gate_ptr = gate_ld = 0
+        if gate is not None:
+            _dense(gate, "gate", torch.float32)
+            if gate.shape[0] != n or gate_col + width > gate.shape[1]:
+                raise KernelError("attention_talk: gate has a row per token and heads * head_dim columns from gate_col")
+            gate_ptr, gate_ld = gate.data_ptr() + 4 * int(gate_col), gate.shape[1]
+        self.launches += 1
+        _check(self._mix_lib().ifb_attention_talk(
+            q.data_ptr(), _code(q), kv_pages.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), cu_q.data_ptr(),
+            seq_lens.data_ptr(), _ptr(talk), _code(talk) if talk is not None else 0, gate_ptr, gate_ld, out.data_ptr(), n, r,
+            num_heads, num_kv_heads, head_dim, kv_pages.shape[3], int(chunk or 0), float(scale), float(slope_exponent or 0.0),
+            self._stream()), "attention_talk")
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):

@@ -5,3 +5,4 @@ from .registry import (  # noqa: F401
     config_from_dict, read_config, plan_for,
 )
 from . import qwen3  # noqa: F401  (registers "Qwen3ForCausalLM")
+from . import kafunex  # noqa: F401  (registers "Kafunex")

@@ -46,10 +46,16 @@ def get_architecture(name: str) -> Architecture:
 
 
 def config_from_dict(d: Mapping[str, Any]):
+    """The typed configuration for a config.json mapping.  The architecture is named by
+    ``architectures[0]`` or, in files that name a single one, by the string ``architecture``."""
     archs = d.get("architectures") if isinstance(d, Mapping) else None
-    if not isinstance(archs, (list, tuple)) or not archs:
+    if isinstance(archs, (list, tuple)) and archs:
+        name = archs[0]
+    elif isinstance(d, Mapping) and isinstance(d.get("architecture"), str):
+        name = d["architecture"]
+    else:
         raise ModelConfigError("config.json lacks required key 'architectures'")
-    return get_architecture(archs[0]).config_class.from_dict(d)
+    return get_architecture(name).config_class.from_dict(d)
 
 
 def read_config(model_dir: str):

@@ -1,7 +1,9 @@
 """How a layer's parts are arranged."""
 from __future__ import annotations
 
-from ..config.specs import PreNormBlockSpec
+import torch
+
+from ..config.specs import PostNormBlockSpec, PreNormBlockSpec
 from .registry import Folded, build_part, register_part
 
 
@@ -54,3 +56,62 @@ class PreNormBlock:
 
 
 register_part(PreNormBlockSpec, PreNormBlock)
+
+
+class PostNormBlock:
+    """x += ls1 * norm(mixer(x)); x += ls2 * norm(ffn(x)): the sublayers read the stream itself and the norm
+    (one number as weight) is applied to their result.  Norm, layer scale and addition are one kernel, which in
+    bfloat16 mode also leaves the bfloat16 copy of the stream that the next product reads.  The block hands on
+    no pending delta: x is up to date when it returns."""
+
+    def __init__(self, spec: PostNormBlockSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.mixer = build_part(spec.mixer, weights, runtime)
+        self.mixer_norm = build_part(spec.mixer_norm, weights, runtime)
+        self.mixer_scale = weights[spec.mixer_scale]
+        self.ffn = build_part(spec.ffn, weights, runtime) if spec.ffn is not None else None
+        self.ffn_norm = build_part(spec.ffn_norm, weights, runtime) if spec.ffn is not None else None
+        self.ffn_scale = weights[spec.ffn_scale] if spec.ffn is not None else None
+
+    @property
+    def graph_safe(self):
+        parts = [self.mixer] + ([self.ffn] if self.ffn is not None else [])
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
+    def _input(self, x, ctx):
+        """What the sublayer's products read: x itself in float32 mode, else its bfloat16 copy."""
+        from .model import STREAM_COPY
+        if self.rt.act_dtype == torch.float32:
+            return x
+        h = ctx.shared.get(STREAM_COPY)
+        if h is None or h.shape != x.shape:
+            h = ctx.buffer("stream_copy", x.shape, torch.bfloat16)
+            self.k.cast_rows(x, h)
+            ctx.shared[STREAM_COPY] = h
+        return h
+
+    def _update(self, x, y, norm, scale, ctx):
+        from .model import STREAM_COPY
+        half = None
+        if self.rt.act_dtype == torch.bfloat16:
+            half = ctx.buffer("stream_copy", x.shape, torch.bfloat16)
+        self.k.residual_postnorm(x, y, norm.weight, scale, norm.spec.eps, half)
+        if half is not None:
+            ctx.shared[STREAM_COPY] = half
+
+    def forward(self, x, pending, ctx, call):
+        from .model import STREAM_COPY
+        if pending is not None:                      # a block of another kind ran before and left its last delta
+            if isinstance(pending, Folded):
+                raise TypeError("a post-norm block cannot take a folded norm from the block before it")
+            x.add_(pending)
+            ctx.shared.pop(STREAM_COPY, None)
+        self._update(x, self.mixer.forward(self._input(x, ctx), ctx, call), self.mixer_norm, self.mixer_scale, ctx)
+        if self.ffn is not None:
+            self._update(x, self.ffn.forward(self._input(x, ctx), ctx), self.ffn_norm, self.ffn_scale, ctx)
+        return None
+
+
+register_part(PostNormBlockSpec, PostNormBlock)

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import GatedMLPSpec
+from ..config.specs import DenseMLPSpec, GatedMLPSpec
 from ..errors import ModelConfigError
 from .registry import fold_residual_norm, register_part, unfolded
 
@@ -47,3 +47,30 @@ class GatedMLP:
 
 
 register_part(GatedMLPSpec, GatedMLP)
+
+
+class DenseMLP:
+    """down(act(up(h))) with the activation in the epilogue of the first product; the result is float32."""
+
+    graph_safe = True
+    ACTIVATIONS = ("relu2", "silu", "gelu_tanh")
+
+    def __init__(self, spec: DenseMLPSpec, weights, runtime):
+        if spec.activation not in self.ACTIVATIONS:
+            raise ModelConfigError(f"activation {spec.activation!r}: the dense feed-forward has {', '.join(self.ACTIVATIONS)}")
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.w_up = weights[spec.up_proj]
+        self.w_down = weights[spec.down_proj]
+
+    def forward(self, h, ctx, fold=None):
+        n = h.shape[0]
+        act = ctx.buffer("ffn_act", (n, self.spec.intermediate_size), self.rt.act_dtype)
+        self.k.linear(h, self.w_up, act, epilogue=self.spec.activation)
+        delta = ctx.buffer("delta_ffn", (n, self.spec.hidden_size), torch.float32)
+        self.k.linear(act, self.w_down, delta)
+        return delta
+
+
+register_part(DenseMLPSpec, DenseMLP)

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import EmbeddingSpec, LMHeadSpec, ModelPlan
+from ..config.specs import EmbeddingSpec, LMHeadSpec, ModelPlan, SinusoidEmbeddingSpec
 from .registry import build_part, register_part
 
 
@@ -35,7 +35,38 @@ class LMHead:
         return out
 
 
+class SinusoidEmbedding:
+    """x[t] = table[id_t] + e(p_t) in float32, with e[2i] = sin(p * base^(-2i/width)) and e[2i+1] = the cosine of
+    the same angle; p_t is the token's position in its sequence.  It takes the step's context (``uses_context``)
+    for the positions, and in bfloat16 mode leaves a bfloat16 copy of the rows for the first layer's products
+    (``ctx.shared[STREAM_COPY]``)."""
+
+    uses_context = True
+
+    def __init__(self, spec: SinusoidEmbeddingSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.table = weights[spec.weight]
+        self.k = runtime.kernels
+        i = torch.arange((spec.hidden_size + 1) // 2, dtype=torch.float64)
+        self.inv_freq = torch.pow(torch.tensor(float(spec.base), dtype=torch.float64),
+                                  -2.0 * i / spec.hidden_size).to(runtime.device)
+
+    def forward(self, ids, out, ctx=None):
+        half = None
+        if self.rt.act_dtype == torch.bfloat16:
+            half = ctx.buffer("stream_copy", out.shape, torch.bfloat16)
+            ctx.shared[STREAM_COPY] = half
+        self.k.embed_sinusoid(self.table, ids, ctx.positions, self.inv_freq, out, half)
+        return out
+
+
+# key of ``ctx.shared`` under which a bfloat16 copy of the current residual stream is handed from the part that wrote the
+# stream last (an embedding, a block's residual update) to the part that reads it next
+STREAM_COPY = ("stream_copy",)
+
 register_part(EmbeddingSpec, Embedding)
+register_part(SinusoidEmbeddingSpec, SinusoidEmbedding)
 register_part(LMHeadSpec, LMHead)
 
 
@@ -62,7 +93,10 @@ class DecoderModel:
     def forward(self, ctx):
         n = ctx.num_tokens
         x = ctx.buffer("x", (n, self.plan.hidden_size), torch.float32)
-        self.embedding.forward(ctx.token_ids, x)
+        if getattr(self.embedding, "uses_context", False):
+            self.embedding.forward(ctx.token_ids, x, ctx=ctx)
+        else:
+            self.embedding.forward(ctx.token_ids, x)
         pending = None
         for i, call in enumerate(self.schedule):
             layer = self.layers[call.layer]

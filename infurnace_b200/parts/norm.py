@@ -1,7 +1,7 @@
 """RMSNorm with the residual addition folded in."""
 from __future__ import annotations
 
-from ..config.specs import RMSNormSpec
+from ..config.specs import RMSNormSpec, ScalarRMSNormSpec
 from .registry import register_part
 
 
@@ -25,3 +25,27 @@ class RMSNorm:
 
 
 register_part(RMSNormSpec, RMSNorm)
+
+
+class ScalarRMSNorm:
+    """out = x * rsqrt(mean(x^2) + eps) * g with one number g, as the last norm of a model (``rows``) or
+    before a product.  It runs the RMSNorm kernel with g repeated along the row, which is the same
+    arithmetic element by element.  As the norm of a sublayer's result inside a residual update it is not
+    called at all: the block's update kernel reads ``weight`` and ``spec.eps``."""
+
+    graph_safe = True
+
+    def __init__(self, spec: ScalarRMSNormSpec, weights, runtime):
+        self.spec = spec
+        self.weight = weights[spec.weight].reshape(1).contiguous()
+        self.k = runtime.kernels
+        self._row = None
+
+    def forward(self, x, out, delta=None, rows=None):
+        if self._row is None or self._row.numel() != x.shape[1]:
+            self._row = self.weight.expand(x.shape[1]).contiguous()
+        self.k.rmsnorm(x, self._row, self.spec.eps, out, delta=delta, rows=rows)
+        return out
+
+
+register_part(ScalarRMSNormSpec, ScalarRMSNorm)

@@ -38,7 +38,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=16)
-    ap.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
+    ap.add_argument("--max-requests", type=int, default=4, help="most requests live at a time (state slots)")
     args = ap.parse_args(argv)
     if args.max_tokens < 1:
         ap.error("--max-tokens must be positive")
@@ -55,7 +55,7 @@ def main(argv=None) -> int:
     pool_tokens = -(-args.max_tokens // unit) * unit
     options = EngineOptions(
         dtype=args.dtype, device="cuda", page_size=args.page_size, num_pages=pool_tokens // args.page_size,
-        max_num_seqs=args.max_requests, max_num_batched_tokens=pool_tokens, max_model_len=None)
+        max_num_seqs=args.max_requests, max_num_batched_tokens=pool_tokens, max_model_len=pool_tokens)
     try:
         _progress(f"loading {args.model} ({args.dtype}); kernels are compiled at first use")
         _, plan, runner = build_runner(args.model, options, progress=_progress)

@@ -76,15 +76,16 @@ def normal_values(seed64: int, n: int, mean: float, std: float):
 class _Producer:
     """Makes one tensor when called; knows shape and dtype beforehand."""
 
-    def __init__(self, seed, name, shape, dtype, kernels=None):
+    def __init__(self, seed, name, shape, dtype, kernels=None, init=None):
         self.seed, self.name, self.shape, self.dtype, self.kernels = seed, name, tuple(shape), dtype, kernels
+        self.init = init
 
     def __call__(self):
         import torch
         n = 1
         for s in self.shape:
             n *= s
-        mean, std = moments(self.shape)
+        mean, std = self.init or moments(self.shape)
         if self.kernels is not None:       # made on the device (the same bits), for folders of large models
             t = torch.empty(self.shape, dtype=self.dtype, device="cuda")
             self.kernels.random_normal(t, tensor_seed(self.seed, self.name), mean, std)
@@ -125,8 +126,8 @@ class DeviceRandomWeights(Mapping):
             if spec.kind == "int":
                 raise NotImplementedError("random integer tables")
             from .loader import target_dtype
-            mean, std = moments(spec.shape)
-            stored = self._norm_store if len(spec.shape) == 1 else self._store
+            mean, std = spec.init or moments(spec.shape)
+            stored = self._norm_store if len(spec.shape) <= 1 else self._store
             t = torch.empty(tuple(spec.shape), dtype=stored, device=self._device)
             self._k.random_normal(t, tensor_seed(self._seed, name), mean, std)
             tag = "F32" if stored == torch.float32 else "BF16"
@@ -153,7 +154,8 @@ def write_random_model(config, seed: int, out_dir: str, store_dtype: str = "bflo
     for name, spec in plan.tensors().items():
         if spec.kind == "int":
             raise NotImplementedError("random integer tables")
-        items.append((name, _Producer(seed, name, spec.shape, norm_dt if len(spec.shape) == 1 else mat_dt, kernels)))
+        items.append((name, _Producer(seed, name, spec.shape, norm_dt if len(spec.shape) <= 1 else mat_dt, kernels,
+                                      init=spec.init)))
     write_safetensors(os.path.join(out_dir, "model.safetensors"), items,
                       metadata={"format": "pt", "seed": str(seed)})
     return out_dir

@@ -70,6 +70,16 @@ class ReferenceKernels:
             half = y.shape[1] // 2
             g, u = y[:, :half], y[:, half:]
             y = g * torch.sigmoid(g) * u
+        elif epilogue == "relu2":
+            y = torch.relu(y) ** 2
+        elif epilogue == "silu":
+            y = y * torch.sigmoid(y)
+        elif epilogue == "sigmoid":
+            y = torch.sigmoid(y)
+        elif epilogue == "gelu_tanh":
+            y = 0.5 * y * (1 + torch.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+        elif epilogue != "none":
+            raise ValueError(epilogue)
         out.copy_(y.to(out.dtype))
 
     def can_fold_norm(self, n, dtype, w, epilogue="none"):
@@ -184,6 +194,98 @@ class ReferenceKernels:
             p = torch.softmax(s.float(), dim=-1).to(self.cd)
             o = torch.einsum("hnk,khd->nhd", p, v)
             out[q0:q1] = o.reshape(n, nq * d).to(out.dtype)
+
+    # ------------------------------------------------------------------ post-norm sublayers, recurrence, talking attention
+    def embed_sinusoid(self, table, ids, positions, inv_freq, out, half=None):
+        """out[n] = table[ids[n]] + e, e[2i] = sin(positions[n] * inv_freq[i]), e[2i+1] = cos of that angle."""
+        ang = positions.to(torch.float64)[:, None] * inv_freq.to(torch.float64)[None, :]
+        e = torch.stack((ang.sin(), ang.cos()), dim=-1).flatten(-2)[:, : out.shape[1]]
+        out.copy_((table[ids.long()].to(torch.float64) + e).to(out.dtype))
+        if half is not None:
+            half.copy_(out.to(half.dtype))
+
+    def residual_postnorm(self, x, y, g, scale, eps, half=None):
+        """x += y / sqrt(mean(y^2) + eps) * g * scale."""
+        v = y.to(self.cd)
+        x.add_((v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps) * g.to(self.cd).reshape(()) * scale.to(self.cd)).to(x.dtype))
+        if half is not None:
+            half.copy_(x.to(half.dtype))
+
+    def cast_rows(self, x, out):
+        out.copy_(x.to(out.dtype))
+
+    def wide_norm_store(self, proj, q_width, k_width, v_col, head_dim, q_weight, k_weight, eps, q_out, slot_mapping, kv_pages):
+        """q_out = whole-row RMSNorm of proj[:, :q_width] times q_weight; key page = the same of the next k_width
+        columns; value page = those columns as they are (v_col < 0) or proj[:, v_col : v_col + k_width]."""
+        def norm(t, w):
+            return t if w is None else t / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w.to(self.cd)
+        q = proj[:, :q_width].to(self.cd)
+        k = proj[:, q_width: q_width + k_width].to(self.cd)
+        v = k if v_col < 0 else proj[:, v_col: v_col + k_width].to(self.cd)
+        q_out.copy_(norm(q, q_weight).to(q_out.dtype))
+        if slot_mapping is None:
+            return
+        ps, g = kv_pages.shape[3], k_width // head_dim
+        kn = norm(k, k_weight).to(kv_pages.dtype).view(-1, g, head_dim)
+        vv = v.to(kv_pages.dtype).view(-1, g, head_dim)
+        for n in range(proj.shape[0]):
+            s = int(slot_mapping[n])
+            if s >= 0:
+                kv_pages[s // ps, 0, :, s % ps, :] = kn[n]
+                kv_pages[s // ps, 1, :, s % ps, :] = vv[n]
+
+    def gated_scan_slabs(self, dim, vdim):
+        return 1
+
+    def gated_scan(self, proj, q_col, f_col, v_col, bias, lower, norm_weight, eps, state, state_slots, cu_q, seq_lens, out,
+                   heads, dim, vdim, raw=None):
+        """Token by token for each request r (rows cu_q[r] .. cu_q[r+1]-1; seq_lens[r] == 0: padding, skipped), on the
+        state rows state[state_slots[r]]: S = f[:, None] * S + (1 - f)[:, None] * v[None, :], o = S^T q, with
+        q = silu(q_raw), f = lower + (1 - lower) * sigmoid(f_raw + bias); out = o / rms(o) * norm_weight per head."""
+        hd, hv = heads * dim, heads * vdim
+        lo, b, nw = lower.to(self.cd), bias.to(self.cd), norm_weight.to(self.cd)
+        for r in range(seq_lens.numel()):
+            if int(seq_lens[r]) <= 0:
+                continue
+            S = state[int(state_slots[r])].to(self.cd)
+            for t in range(int(cu_q[r]), int(cu_q[r + 1])):
+                qr = proj[t, q_col: q_col + hd].to(self.cd)
+                q = (qr * torch.sigmoid(qr)).view(heads, dim)
+                f = (lo + (1 - lo) * torch.sigmoid(proj[t, f_col: f_col + hd].to(self.cd) + b)).view(heads, dim)
+                v = proj[t, v_col: v_col + hv].to(self.cd).view(heads, vdim)
+                S = f[:, :, None] * S + (1 - f)[:, :, None] * v[:, None, :]
+                o = torch.einsum("hde,hd->he", S, q)
+                o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * nw
+                out[t] = o.reshape(hv).to(out.dtype)
+            state[int(state_slots[r])] = S.to(state.dtype)
+
+    def attention_talk(self, q, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
+                       chunk=0, slope_exponent=0.0, talk=None, gate=None, gate_col=0, max_q_len=0):
+        """Per request, the query at position p sees keys (p // chunk) * chunk .. p (chunk 0: 0 .. p) from the pages:
+        a[j] = scale * q_j . k - slope_j * (p - s); b = talk @ a over the heads; softmax over the keys; o = P V;
+        out = o * sigmoid(gate)."""
+        H, G, d = num_heads, num_kv_heads, head_dim
+        ps = kv_pages.shape[3]
+        slopes = torch.tensor([2.0 ** (-slope_exponent * (j + 1) / H) if slope_exponent else 0.0 for j in range(H)], dtype=self.cd)
+        for r in range(seq_lens.numel()):
+            q0, q1, L = int(cu_q[r]), int(cu_q[r + 1]), int(seq_lens[r])
+            if L <= 0:
+                out[q0:q1] = 0
+                continue
+            for t in range(q0, q1):
+                p = L - (q1 - q0) + (t - q0)
+                first = (p // chunk) * chunk if chunk else 0
+                pos = torch.arange(first, p + 1)
+                pages = block_tables[r].long()[pos // ps]
+                k = kv_pages[pages, 0, :, pos % ps, :].to(self.cd).repeat_interleave(H // G, dim=1)      # [keys, H, d]
+                v = kv_pages[pages, 1, :, pos % ps, :].to(self.cd).repeat_interleave(H // G, dim=1)
+                a = torch.einsum("hd,shd->hs", q[t].to(self.cd).view(H, d), k) * scale - slopes[:, None] * (p - pos).to(self.cd)[None]
+                if talk is not None:
+                    a = talk.to(self.cd) @ a
+                o = torch.einsum("hs,shd->hd", torch.softmax(a, dim=-1), v).reshape(H * d)
+                if gate is not None:
+                    o = o * torch.sigmoid(gate[t, gate_col: gate_col + H * d].to(self.cd))
+                out[t] = o.to(out.dtype)
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):

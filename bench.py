@@ -41,6 +41,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -571,6 +572,175 @@ def run_ours(args):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# --designs: the post-norm recurrent/attention design (Kafunex) beside Qwen3 at equal sizes
+FP32_LANES_PER_SM = 128            # float32 multiply-adds an SM issues per clock
+
+
+def design_configs(size):
+    """(Kafunex config.json mapping, Qwen3 config.json mapping) of about the same width, depth and parameter count.
+    Layer pattern of the first: attention, recurrence, recurrence, attention, ..."""
+    W, layers, H, G, d, rh, rd, rv, ff, chunk = {
+        "s": (1024, 8, 16, 4, 64, 8, 64, 128, 3072, 512),
+        "m": (2048, 8, 16, 4, 128, 16, 64, 128, 6144, 1024),
+        "l": (4096, 8, 32, 8, 128, 32, 64, 128, 12288, 1024),
+    }[size]
+    vocab = 32768
+    entries, params = [], 0
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff}
+        if i % 4 in (0, 3):
+            entries.append({"type": "attention", "mixer": {"dim": d, "heads": H, "kv_heads": G, "mask": {"size": chunk},
+                                                          "scale": d ** -0.5, "vdim": d}, "mlp": mlp})
+            params += W * (3 * H * d + G * d) + 2 * W * ff
+        else:
+            entries.append({"type": "hgrn2", "mixer": {"dim": rd, "heads": rh, "vdim": rv}, "mlp": mlp})
+            params += W * (2 * rh * rd + 2 * rh * rv) + 2 * W * ff
+    kaf = {"architecture": "Kafunex", "layers": entries, "norm": {"eps": 1e-5}, "vocab": vocab, "width": W}
+    attn = W * (2 * H * d + 2 * G * d)
+    inter = max(256, round((params / layers - attn) / (3 * W) / 256) * 256)
+    qwen = {"architectures": ["Qwen3ForCausalLM"], "hidden_size": W, "num_hidden_layers": layers, "num_attention_heads": H,
+            "num_key_value_heads": G, "head_dim": d, "intermediate_size": inter, "vocab_size": vocab, "rope_theta": 1e6,
+            "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 8192}
+    return kaf, qwen
+
+
+class DesignTimer(KernelClassTimer):
+    """Events around every launch of either design's kernels, with what each launch has to do at the least: tensor-core
+    flops, float32 flops on the ordinary pipes, and bytes of device memory.  ``pairs``: (query, visible key) pairs of
+    one attention call of the step, set by the caller (the step's composition decides it)."""
+    METHODS = KernelClassTimer.METHODS + ("embed_sinusoid", "residual_postnorm", "cast_rows", "wide_norm_store", "gated_scan",
+                                          "attention_talk")
+
+    def __init__(self, kernels, vocab, pairs, key_bytes):
+        super().__init__(kernels, vocab)
+        self.pairs, self.key_bytes = pairs, key_bytes
+        self.work = []            # per record: (tensor flops, float32 flops, bytes)
+
+    def _classify(self, name, a, kw):
+        tf = ff = by = 0
+        cls = "rest"
+        if name == "paged_attention":
+            cls, tf, by = "attention", 4 * a[1] * a[3] * self.pairs, self.key_bytes
+        elif name == "attention_talk":
+            H, d = a[1], a[3]
+            cls, tf, ff, by = "attention", 4 * H * d * self.pairs, 2 * H * H * self.pairs, self.key_bytes
+        elif name == "gated_scan":
+            proj, out, heads, dim, vdim = a[0], a[12], a[13], a[14], a[15]
+            n = proj.shape[0]
+            cls, ff = "recurrence", 6 * n * heads * dim * vdim
+            by = proj.numel() * 4 + out.numel() * out.element_size() + 2 * a[11].numel() * heads * dim * vdim * 4
+        elif name in ("linear", "linear_residual_norm"):
+            x, w = a[0], a[1]
+            cls = "lm_head" if w.shape[0] == self.vocab else "products"
+            tf, by = 2 * x.shape[0] * w.numel(), w.numel() * w.element_size()
+        self.work.append((tf, ff, by))
+        return cls, by, tf
+
+    def report_bounds(self, steps, tc_peak, fp32_peak, hbm_peak):
+        """Per class: ms a step, launches, and the bound: the slowest of (tensor flops / tensor peak, float32 flops /
+        float32 peak, bytes / copy bandwidth), summed over the launches, over the time measured."""
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for (cls, _, _, s, e), (tf, ff, by) in zip(self.records, self.work):
+            d = out.setdefault(cls, {"ms": 0.0, "bound_ms": 0.0, "launches": 0, "tensor_flops": 0, "fp32_flops": 0, "bytes": 0})
+            d["ms"] += s.elapsed_time(e)
+            d["bound_ms"] += 1e3 * max(tf / (tc_peak * 1e12), ff / (fp32_peak * 1e12), by / (hbm_peak * 1e9))
+            d["launches"] += 1
+            d["tensor_flops"] += tf; d["fp32_flops"] += ff; d["bytes"] += by
+        rep = {}
+        for cls, d in out.items():
+            r = {"ms_per_step": round(d["ms"] / steps, 4), "launches_per_step": d["launches"] // steps}
+            if d["bound_ms"]:
+                r["of_bound"] = round(d["bound_ms"] / d["ms"], 4)
+                which = max((d["tensor_flops"] / tc_peak / 1e3, "tensor"), (d["fp32_flops"] / fp32_peak / 1e3, "fp32"),
+                            (d["bytes"] / hbm_peak, "hbm"))[1]
+                r["bound"] = which
+            rep[cls] = r
+        return rep
+
+
+def visible_pairs(plan_layer_chunk, positions):
+    """Sum over query positions of the keys each sees: all earlier ones, or those of its own chunk."""
+    if not plan_layer_chunk:
+        return sum(p + 1 for p in positions)
+    return sum(p % plan_layer_chunk + 1 for p in positions)
+
+
+def run_designs(args):
+    """Prefill (2,048 tokens in one step) and decode (batch 8, each request 2,048 tokens in) of the Kafunex design and
+    of Qwen3 at equal width, depth and parameter count, random weights, bfloat16; and where the time of each goes by
+    class of kernel, against the least each class has to do.  One JSON line."""
+    import torch
+    from infurnace_b200.engine import Engine, EngineOptions
+    from infurnace_b200.engine.runner import StepEntry
+    hbm_peak, tc_peak, peak_src = read_peaks()
+    props = torch.cuda.get_device_properties(0)
+    clock_ghz = 1.965
+    fp32_peak = props.multi_processor_count * FP32_LANES_PER_SM * 2 * clock_ghz / 1e3          # TFLOP/s, nominal
+    batch, context = 8, 2048
+    sampler = ClockSampler()
+    sampler.start()
+    results = {}
+    for size in args.design_sizes.split(","):
+        kaf, qwen = design_configs(size)
+        for design, conf in (("kafunex", kaf), ("qwen3", qwen)):
+            pool = batch * (context + 64) + PREFILL_TOKENS + 64
+            opts = EngineOptions(dtype="bfloat16", page_size=16, num_pages=pool // 16, max_num_seqs=batch,
+                                 max_num_batched_tokens=PREFILL_TOKENS, max_model_len=context + 64)
+            eng = Engine.from_random(conf, 1, opts)
+            runner, plan = eng.runner, eng.plan
+            vocab = plan.vocab_size
+            params = sum(math.prod(t.shape) for t in plan.tensors().values())
+            chunks = [getattr(getattr(l, "mixer", None), "chunk", None) for l in plan.layers]
+            chunk = next((c for c in chunks if c), None)
+            ms = time_prefill(runner, vocab, 3)
+            pre = statistics.median(ms)
+            rids = fill_contexts(runner, batch, context)
+            randomize_pages(runner)
+            total, launches, per = time_decode(runner, rids, vocab, args.steps, max(3, args.warmup))
+            release(runner, rids)
+            dec = statistics.median(per)
+            r = {"params_m": round(params / 1e6, 1), "prefill_ms": round(pre, 3), "prefill_tok_s": round(PREFILL_TOKENS / pre * 1e3),
+                 "decode_ms": round(dec, 4), "decode_tok_s": round(batch / dec * 1e3), "decode_launches": launches // args.steps}
+            # where the time goes: an eager pass with events around every launch
+            K = runner.rt.kernels
+            graphs, runner.use_graphs = runner.use_graphs, False
+            G_, d_ = (conf["layers"][0]["mixer"]["kv_heads"], conf["layers"][0]["mixer"]["dim"]) if design == "kafunex" \
+                else (conf["num_key_value_heads"], conf["head_dim"])
+            toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(2)).tolist()
+            runner.cache.add_request("kp")
+            with DesignTimer(K, vocab, visible_pairs(chunk, range(PREFILL_TOKENS)), 2 * PREFILL_TOKENS * G_ * d_ * 2) as t:
+                torch.cuda.synchronize()
+                hold_the_device(20.0)
+                runner.step([StepEntry("kp", toks, [PREFILL_TOKENS - 1])])
+                r["prefill_kernels"] = t.report_bounds(1, tc_peak, fp32_peak, hbm_peak)
+            runner.cache.free_request("kp")
+            rids = fill_contexts(runner, batch, context, prefix="k")
+            zeros = [0.0] * batch
+            step = lambda: runner.step_and_sample([StepEntry(x, [1], [0]) for x in rids], zeros, zeros)      # noqa: E731
+            step()
+            seen = visible_pairs(chunk, [context + 1])
+            with DesignTimer(K, vocab, batch * seen, batch * seen * G_ * d_ * 2 * 2) as t:
+                for _ in range(3):
+                    torch.cuda.synchronize()
+                    hold_the_device()
+                    step()
+                r["decode_kernels"] = t.report_bounds(3, tc_peak, fp32_peak, hbm_peak)
+            release(runner, rids)
+            runner.use_graphs = graphs
+            results.setdefault(size, {})[design] = r
+            del eng, runner
+            torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "designs_prefill_and_decode", "dtype": "bfloat16", "data": "synthetic (random weights)",
+                      "prefill_tokens": PREFILL_TOKENS, "decode": {"batch": batch, "context": context},
+                      "peaks": {"hbm_gbs": hbm_peak, "tensor_tflops": tc_peak, "fp32_tflops_nominal": round(fp32_peak, 1),
+                                "source": peak_src}, "sizes": results, "clocks": clocks}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -586,6 +756,9 @@ def main():
     ap.add_argument("--mode", default="all", choices=("all", "decode", "prefill", "generate"),
                     help="decode / prefill / generate: only that part, on a pool just large enough (for profiling a small case)")
     ap.add_argument("--eager", action="store_true", help="launch every kernel of a decode step instead of replaying a graph")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the default workload: the Kafunex design beside Qwen3 at equal sizes (prefill and decode)")
+    ap.add_argument("--design-sizes", default="s,m", help="with --designs: which of the sizes s, m, l (commas between)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -596,6 +769,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.designs:
+        return run_designs(args)
     return run_ours(args)
 
 

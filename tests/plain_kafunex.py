@@ -123,3 +123,24 @@ def forward(cfg, w, tokens, return_layers=False):
     if return_layers:
         return logits, torch.stack(after)
     return logits
+
+
+def read_model(model_dir):
+    """(config.json as a dict, name -> tensor) of a model folder."""
+    import json
+    import os
+    from safetensors.torch import load_file
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, load_file(os.path.join(model_dir, "model.safetensors"))
+
+
+def greedy(cfg, w, prompt, n):
+    """n tokens by argmax (lowest index among equals), recomputing the whole sequence each time."""
+    toks = list(prompt)
+    out = []
+    for _ in range(n):
+        nxt = int(torch.argmax(forward(cfg, w, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out

@@ -679,7 +679,7 @@ def run_designs(args):
     props = torch.cuda.get_device_properties(0)
     clock_ghz = 1.965
     fp32_peak = props.multi_processor_count * FP32_LANES_PER_SM * 2 * clock_ghz / 1e3          # TFLOP/s, nominal
-    batch, context = 8, 2048
+    batch, context = 8, 2040          # the next position stands near the end of a chunk of 512 or 1,024
     sampler = ClockSampler()
     sampler.start()
     results = {}
@@ -721,7 +721,7 @@ def run_designs(args):
             zeros = [0.0] * batch
             step = lambda: runner.step_and_sample([StepEntry(x, [1], [0]) for x in rids], zeros, zeros)      # noqa: E731
             step()
-            seen = visible_pairs(chunk, [context + 1])
+            seen = visible_pairs(chunk, [context + 1])          # keys a decoded token sees
             with DesignTimer(K, vocab, batch * seen, batch * seen * G_ * d_ * 2 * 2) as t:
                 for _ in range(3):
                     torch.cuda.synchronize()

@@ -1,0 +1,332 @@
+// Attention with the heads' scores mixed before the softmax (see attention_talk.cu for the arithmetic), bfloat16
+// operands on the tensor cores (mma.sync m16n8k16, float32 accumulation), for prompts, portions and decoded tokens.
+//
+// A CTA owns a tile of 16 query tokens of one request and a group of NW output heads, one per warp.  Keys of the
+// tile's chunk are taken 32 at a time:
+//   1. K of every key/value head and V of the group's key/value heads come into shared memory (16-byte async copies);
+//   2. the warps form the raw scores of ALL query heads, S_h = Q_h K_g^T (the mixing needs every head's score of a
+//      (query, key) pair), scale them, subtract the distance bias and leave them in shared memory in float32;
+//   3. the block mixes: for its pair (query, key) a thread forms b[o] = sum_h talk[o][h] * a[h] for the group's
+//      heads o, in float32 on the ordinary pipes (the scores are never rounded);
+//   4. warp w carries head o = group * NW + w: running maximum and sum per row, P rounded to bfloat16 as the A
+//      operand of O += P V, V read transposed from shared memory.
+// With more query heads than NW the groups are CTAs of their own, each of which forms the raw scores again (tensor
+// work that is cheap beside step 3, whose cost does not depend on the split).  The output is multiplied by
+// sigmoid(gate) and stored as bfloat16.  Head sizes 16, 32, 64, 128.
+#include "common.cuh"
+#include <math.h>
+#include <mma.h>
+
+typedef __nv_bfloat16 bf16;
+
+struct TalkMmaArgs {
+  const bf16* q;            // [tokens][H * D]
+  const bf16* pages;        // [pages][2][G][page_size][D]
+  const int* block_tables;
+  int bt_stride;
+  const int* cu_q;
+  const int* seq_lens;
+  const void* talk;         // [H][H] or null
+  int talk_dtype;
+  const float* gate;        // row n at gate + n * gate_ld; or null
+  int gate_ld;
+  bf16* out;                // [tokens][H * D]
+  int n_tokens, n_req, H, G, page_size, chunk;
+  float scale, slope_exp;
+};
+
+constexpr int TM_ROWS = 16, TM_KEYS = 32;
+
+__device__ __forceinline__ uint32_t tm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tm_cp16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(tm_smem(dst)), "l"(src));
+}
+__device__ __forceinline__ void tm_cp_wait() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory"); }
+__device__ __forceinline__ void tm_ldsm4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(tm_smem(p)));
+}
+__device__ __forceinline__ void tm_ldsm4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(tm_smem(p)));
+}
+__device__ __forceinline__ void tm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t tm_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Shared memory, in this order: Q [H][16][D + 8] bf16, K [G][32][D + 8] bf16, V [GV][32][D + 8] bf16 (GV: key/value
+// heads of the group), S [H][16][32] float, M [NW][16][32] float, talk^T [H][NW] float.
+template <int D, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
+attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
+  extern __shared__ __align__(16) unsigned char tm_raw[];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  constexpr int LD = D + 8;                               // row pitch in elements: 16-byte aligned, no bank conflicts
+  const int H = a.H, G = a.G, rep = H / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  // which (request, tile) this CTA is
+  int r = -1, tile = 0;
+  {
+    int left = blockIdx.x;
+    for (int i = 0; i < a.n_req; ++i) {
+      const int ql = a.seq_lens[i] > 0 ? a.cu_q[i + 1] - a.cu_q[i] : 0;     // a request of length 0 is padding
+      const int tiles = (ql + TM_ROWS - 1) / TM_ROWS;
+      if (left < tiles) { r = i; tile = left; break; }
+      left -= tiles;
+    }
+  }
+  if (r < 0) return;
+  const int q_len = a.cu_q[r + 1] - a.cu_q[r];
+  const int q0 = a.cu_q[r] + tile * TM_ROWS;
+  const int rows = min(TM_ROWS, q_len - tile * TM_ROWS);
+  const int p0 = a.seq_lens[r] - q_len + tile * TM_ROWS;            // position of the tile's first query
+  const int p_last = p0 + rows - 1;
+  const int o0 = blockIdx.y * NW;                                   // first head of the group
+  const int heads_here = min(NW, H - o0);
+  const int g_lo = o0 / rep, g_hi = (o0 + heads_here - 1) / rep, GV = g_hi - g_lo + 1;
+
+  bf16* Qs = reinterpret_cast<bf16*>(tm_raw);
+  bf16* Ks = Qs + (size_t)H * TM_ROWS * LD;
+  bf16* Vs = Ks + (size_t)G * TM_KEYS * LD;
+  float* Ss = reinterpret_cast<float*>(Vs + (size_t)gv_max * TM_KEYS * LD);
+  float* Ms = Ss + (size_t)H * TM_ROWS * TM_KEYS;
+  float* Tt = Ms + (size_t)NW * TM_ROWS * TM_KEYS;                  // [H][NW]: talk[o0 + o][h] at Tt[h * NW + o]
+
+  constexpr int CH = D / 8;                                         // 16-byte pieces of a head row
+  for (int idx = tid; idx < H * TM_ROWS * CH; idx += NW * 32) {
+    const int c = idx % CH, i = (idx / CH) % TM_ROWS, h = idx / (CH * TM_ROWS);
+    bf16* dst = Qs + ((size_t)h * TM_ROWS + i) * LD + c * 8;
+    if (i < rows) tm_cp16(dst, a.q + (size_t)(q0 + i) * H * D + (size_t)h * D + c * 8);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+  }
+  if (a.talk)
+    for (int idx = tid; idx < H * NW; idx += NW * 32) {
+      const int h = idx / NW, o = idx % NW;
+      Tt[idx] = o < heads_here ? load_as_f32(a.talk, a.talk_dtype, (size_t)(o0 + o) * H + h) : 0.f;
+    }
+
+  const int chunk = a.chunk;
+  const int first = chunk > 0 ? (p0 / chunk) * chunk : 0;           // the first key any row of the tile sees
+  const int* bt = a.block_tables + (size_t)r * a.bt_stride;
+  const size_t head_stride = (size_t)a.page_size * D, page_stride = 2 * (size_t)G * head_stride;
+  const int rl = lane >> 2, cl = (lane & 3) * 2;                    // this lane's row and first column in an 8-wide tile
+  const int pr0 = p0 + rl, pr1 = p0 + rl + 8;                       // positions of its two rows
+  const int lo0 = chunk > 0 ? (pr0 / chunk) * chunk : 0, lo1 = chunk > 0 ? (pr1 / chunk) * chunk : 0;
+  const bool row0 = rl < rows, row1 = rl + 8 < rows;
+
+  float O[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) { O[n][0] = O[n][1] = O[n][2] = O[n][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  for (int k0 = first; k0 <= p_last; k0 += TM_KEYS) {
+    // ---- 1. keys and values of this tile
+    for (int idx = tid; idx < (G + GV) * TM_KEYS * CH; idx += NW * 32) {
+      const int c = idx % CH, j = (idx / CH) % TM_KEYS, gg = idx / (CH * TM_KEYS);
+      const bool is_v = gg >= G;
+      const int g = is_v ? g_lo + (gg - G) : gg;
+      bf16* dst = (is_v ? Vs + ((size_t)(gg - G) * TM_KEYS + j) * LD : Ks + ((size_t)g * TM_KEYS + j) * LD) + c * 8;
+      const int key = k0 + j;
+      if (key <= p_last) {
+        const bf16* src = a.pages + (size_t)bt[key / a.page_size] * page_stride + ((size_t)(is_v ? G : 0) + g) * head_stride +
+                          (size_t)(key % a.page_size) * D + c * 8;
+        tm_cp16(dst, src);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    tm_cp_wait();
+    __syncthreads();
+    // ---- 2. raw scores of every query head
+    for (int h = warp; h < H; h += NW) {
+      float acc[4][4];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+      const bf16* qh = Qs + (size_t)h * TM_ROWS * LD;
+      const bf16* kg = Ks + (size_t)(h / rep) * TM_KEYS * LD;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t af[4];
+        tm_ldsm4(af, qh + (size_t)(lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int n2 = 0; n2 < 2; ++n2) {                 // two 8-key tiles per load
+          uint32_t bfr[4];
+          tm_ldsm4(bfr, kg + (size_t)(n2 * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+          tm_mma(acc[2 * n2], af, bfr[0], bfr[1]);
+          tm_mma(acc[2 * n2 + 1], af, bfr[2], bfr[3]);
+        }
+      }
+      const float slope = a.slope_exp > 0.f ? exp2f(-a.slope_exp * (float)(h + 1) / (float)H) : 0.f;
+      float* sh = Ss + (size_t)h * TM_ROWS * TM_KEYS;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = n * 8 + cl, key = k0 + col;
+        float2 v0 = make_float2(acc[n][0] * a.scale - slope * (float)(pr0 - key), acc[n][1] * a.scale - slope * (float)(pr0 - key - 1));
+        float2 v1 = make_float2(acc[n][2] * a.scale - slope * (float)(pr1 - key), acc[n][3] * a.scale - slope * (float)(pr1 - key - 1));
+        *reinterpret_cast<float2*>(sh + rl * TM_KEYS + col) = v0;
+        *reinterpret_cast<float2*>(sh + (rl + 8) * TM_KEYS + col) = v1;
+      }
+    }
+    __syncthreads();
+    // ---- 3. the heads' scores of each (query, key) pair mixed, for the group's heads
+    const float* Sc = Ss + (size_t)o0 * TM_ROWS * TM_KEYS;          // without mixing: the group's own scores
+    if (a.talk) {
+      for (int pair = tid; pair < TM_ROWS * TM_KEYS; pair += NW * 32) {
+        float b[NW];
+#pragma unroll
+        for (int o = 0; o < NW; ++o) b[o] = 0.f;
+        for (int h = 0; h < H; ++h) {
+          const float s = Ss[(size_t)h * TM_ROWS * TM_KEYS + pair];
+          const float* t = Tt + h * NW;
+#pragma unroll
+          for (int o = 0; o < NW; ++o) b[o] = fmaf(t[o], s, b[o]);
+        }
+#pragma unroll
+        for (int o = 0; o < NW; ++o) Ms[o * TM_ROWS * TM_KEYS + pair] = b[o];
+      }
+      __syncthreads();
+      Sc = Ms;
+    }
+    // ---- 4. softmax step and O += P V for this warp's head
+    if (warp < heads_here) {
+      const float* sw = Sc + (size_t)warp * TM_ROWS * TM_KEYS;
+      float s[4][4];
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const int col = n * 8 + cl, key = k0 + col;
+        const float2 v0 = *reinterpret_cast<const float2*>(sw + rl * TM_KEYS + col);
+        const float2 v1 = *reinterpret_cast<const float2*>(sw + (rl + 8) * TM_KEYS + col);
+        s[n][0] = (row0 && key >= lo0 && key <= pr0) ? v0.x : -INFINITY;
+        s[n][1] = (row0 && key + 1 >= lo0 && key + 1 <= pr0) ? v0.y : -INFINITY;
+        s[n][2] = (row1 && key >= lo1 && key <= pr1) ? v1.x : -INFINITY;
+        s[n][3] = (row1 && key + 1 >= lo1 && key + 1 <= pr1) ? v1.y : -INFINITY;
+        mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;     // a row that has seen no key yet
+      const float c0 = expf(m0 - b0), c1 = expf(m1 - b1);
+      m0 = n0; m1 = n1;
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t pa[2][4];
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const float e0 = expf(s[n][0] - b0), e1 = expf(s[n][1] - b0), e2 = expf(s[n][2] - b1), e3 = expf(s[n][3] - b1);
+        sum0 += e0 + e1; sum1 += e2 + e3;
+        pa[n >> 1][(n & 1) * 2] = tm_pack(e0, e1);
+        pa[n >> 1][(n & 1) * 2 + 1] = tm_pack(e2, e3);
+      }
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      l0 = l0 * c0 + sum0; l1 = l1 * c1 + sum1;
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) { O[n][0] *= c0; O[n][1] *= c0; O[n][2] *= c1; O[n][3] *= c1; }
+      const bf16* vg = Vs + (size_t)((o0 + warp) / rep - g_lo) * TM_KEYS * LD;
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+        for (int n2 = 0; n2 < D / 16; ++n2) {            // two 8-wide tiles of the head per load
+          uint32_t bfr[4];
+          tm_ldsm4_t(bfr, vg + (size_t)(kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + n2 * 16 + (lane >> 4) * 8);
+          tm_mma(O[2 * n2], pa[kk], bfr[0], bfr[1]);
+          tm_mma(O[2 * n2 + 1], pa[kk], bfr[2], bfr[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (warp >= heads_here) return;
+  const float i0 = 1.f / l0, i1 = 1.f / l1;
+  const int head = o0 + warp;
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) {
+    const int col = head * D + n * 8 + cl;
+    if (row0) {
+      float x = O[n][0] * i0, y = O[n][1] * i0;
+      if (a.gate) {
+        const float* gp = a.gate + (size_t)(q0 + rl) * a.gate_ld + col;
+        x *= 1.f / (1.f + expf(-gp[0])); y *= 1.f / (1.f + expf(-gp[1]));
+      }
+      *reinterpret_cast<uint32_t*>(a.out + (size_t)(q0 + rl) * H * D + col) = tm_pack(x, y);
+    }
+    if (row1) {
+      float x = O[n][2] * i1, y = O[n][3] * i1;
+      if (a.gate) {
+        const float* gp = a.gate + (size_t)(q0 + rl + 8) * a.gate_ld + col;
+        x *= 1.f / (1.f + expf(-gp[0])); y *= 1.f / (1.f + expf(-gp[1]));
+      }
+      *reinterpret_cast<uint32_t*>(a.out + (size_t)(q0 + rl + 8) * H * D + col) = tm_pack(x, y);
+    }
+  }
+}
+
+static size_t tm_smem_bytes(int H, int G, int D, int NW, int gv_max) {
+  return ((size_t)H * TM_ROWS + (size_t)(G + gv_max) * TM_KEYS) * (D + 8) * sizeof(bf16) +
+         ((size_t)(H + NW) * TM_ROWS * TM_KEYS + (size_t)H * NW) * sizeof(float);
+}
+static int tm_warps(int H) { return H <= 4 ? 4 : H <= 8 ? 8 : 16; }
+static int tm_gv_max(int H, int G, int NW) {        // key/value heads that a group of NW query heads can touch
+  const int rep = H / G;
+  int most = 1;
+  for (int o0 = 0; o0 < H; o0 += NW) {
+    const int last = (o0 + NW < H ? o0 + NW : H) - 1;
+    most = max(most, last / rep - o0 / rep + 1);
+  }
+  return most;
+}
+
+// Whether the tensor-core kernel takes these sizes (else the caller runs the plain one): bfloat16, head size 16, 32, 64
+// or 128, and a tile's shared memory within an SM's.
+IFB_EXPORT int ifb_attention_talk_mma_fits(int H, int G, int D) {
+  if (H < 1 || G < 1 || H % G || (D != 16 && D != 32 && D != 64 && D != 128)) return 0;
+  const int NW = tm_warps(H);
+  return tm_smem_bytes(H, G, D, NW, tm_gv_max(H, G, NW)) <= 220 * 1024 ? 1 : 0;
+}
+
+template <int D, int NW>
+static int tm_launch(const TalkMmaArgs& a, cudaStream_t s) {
+  const int gv_max = tm_gv_max(a.H, a.G, NW);
+  const size_t smem = tm_smem_bytes(a.H, a.G, D, NW, gv_max);
+  IFB_ALLOW_SMEM((attention_talk_mma_kernel<D, NW>), smem);
+  dim3 grid((a.n_tokens + TM_ROWS - 1) / TM_ROWS + a.n_req, (a.H + NW - 1) / NW);
+  return ifb_launch(attention_talk_mma_kernel<D, NW>, grid, dim3(NW * 32), smem, s, a, gv_max);
+}
+
+template <int D>
+static int tm_by_heads(const TalkMmaArgs& a, cudaStream_t s) {
+  switch (tm_warps(a.H)) {
+    case 4: return tm_launch<D, 4>(a, s);
+    case 8: return tm_launch<D, 8>(a, s);
+    default: return tm_launch<D, 16>(a, s);
+  }
+}
+
+IFB_EXPORT int ifb_attention_talk_mma(const void* q, const void* pages, const int* block_tables, int bt_stride, const int* cu_q,
+                                      const int* seq_lens, const void* talk, int talk_dtype, const float* gate, int gate_ld,
+                                      void* out, int n_tokens, int n_req, int H, int G, int d, int page_size, int chunk,
+                                      float scale, float slope_exp, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_req <= 0) return IFB_OK;
+  if (!ifb_attention_talk_mma_fits(H, G, d)) return IFB_ERR_SIZE;
+  if (page_size < 1 || chunk < 0) return IFB_ERR_ARG;
+  if (((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3)) return IFB_ERR_ALIGN;
+  if (gate && ((uintptr_t)gate & 3)) return IFB_ERR_ALIGN;
+  if (talk && talk_dtype != IFB_F32 && talk_dtype != IFB_BF16) return IFB_ERR_DTYPE;
+  TalkMmaArgs a{(const bf16*)q, (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, talk, talk_dtype, gate, gate_ld,
+                (bf16*)out, n_tokens, n_req, H, G, page_size, chunk, scale, slope_exp};
+  switch (d) {
+    case 16: return tm_by_heads<16>(a, stream);
+    case 32: return tm_by_heads<32>(a, stream);
+    case 64: return tm_by_heads<64>(a, stream);
+    default: return tm_by_heads<128>(a, stream);
+  }
+}

@@ -13,6 +13,13 @@
 // columns than a block has threads (the more rows a thread keeps, the fewer threads a block may have) is split into
 // slabs of columns, a block each; the outputs then go to a float32 scratch and a second kernel normalises them.
 // Everything is float32; proj holds the projections as the product wrote them (float32).
+//
+// Long portions are cut into blocks of GS_BLOCK tokens that run side by side, in three launches: (A) every block is
+// walked from a zero state, which leaves its own contribution Z_b and the product A_b of its gates (per row); (B) a
+// thread per state element carries the state over the blocks, S_(b+1) = A_b * S_b + Z_b, leaving in Z_b's place the
+// state S_b at the block's start, and writes the request's final state to its slot; (C) every block is walked again
+// from S_b, now writing outputs.  Twice the arithmetic of the one-launch walk, for (tokens / GS_BLOCK) times as many
+// blocks in flight.  The result differs from the one-launch walk by rounding only (the recurrence is linear in S).
 #include "common.cuh"
 #include <math.h>
 
@@ -33,7 +40,29 @@ struct GatedScanArgs {
   void* out;               // [tokens][heads * vdim], T
   float* raw;              // [tokens][heads * vdim]: the outputs before the norm, when a head has several slabs (else null)
   int heads, dim, vdim, slabs;
+  int mode;                // 0: a request per block row, from and to its slot.  1: launch A.  2: launch C.
+  int requests;
+  float* z;                // [blocks][heads][dim][vdim]: launch A writes Z_b, launch B turns it into S_b, launch C reads it
+  float* decay;            // [blocks][heads][dim]: A_b
 };
+
+constexpr int GS_BLOCK = 64;       // tokens of a block of the three-launch form (a multiple of GS_GROUP)
+
+// The block of GS_BLOCK tokens that a CTA row is: request, first and last token.  False: the row is beyond the last block.
+__device__ __forceinline__ bool gs_find_block(const GatedScanArgs& a, int row, int& r, int& t0, int& t1) {
+  for (int i = 0; i < a.requests; ++i) {
+    const int ql = a.seq_lens[i] > 0 ? a.cu_q[i + 1] - a.cu_q[i] : 0;
+    const int blocks = (ql + GS_BLOCK - 1) / GS_BLOCK;
+    if (row < blocks) {
+      r = i;
+      t0 = a.cu_q[i] + row * GS_BLOCK;
+      t1 = min(a.cu_q[i + 1], t0 + GS_BLOCK);
+      return true;
+    }
+    row -= blocks;
+  }
+  return false;
+}
 
 constexpr int gs_max_threads(int dmax) { return dmax <= 32 ? 512 : dmax <= 64 ? 256 : 128; }
 
@@ -43,20 +72,29 @@ gated_scan_kernel(GatedScanArgs a) {
   extern __shared__ float sm[];
   ifb_pdl_wait();
   ifb_pdl_trigger();
-  const int r = blockIdx.y, h = blockIdx.x / a.slabs, c0 = (blockIdx.x % a.slabs) * blockDim.x, c = c0 + threadIdx.x;
+  const int h = blockIdx.x / a.slabs, c0 = (blockIdx.x % a.slabs) * blockDim.x, c = c0 + threadIdx.x;
   const int dim = a.dim, vdim = a.vdim;
   const int width = min((int)blockDim.x, vdim - c0);        // columns of this block
-  if (a.seq_lens[r] <= 0) return;
-  const int t0 = a.cu_q[r], t1 = a.cu_q[r + 1];
+  int r = blockIdx.y, t0, t1;
+  if (a.mode == 0) {
+    if (a.seq_lens[r] <= 0) return;
+    t0 = a.cu_q[r]; t1 = a.cu_q[r + 1];
+  } else if (!gs_find_block(a, blockIdx.y, r, t0, t1)) {
+    return;
+  }
   float* qs = sm;                              // [GROUP][DMAX]
   float* fs = qs + GS_GROUP * DMAX;            // [GROUP][DMAX]
   float* vs = fs + GS_GROUP * DMAX;            // [GROUP][threads]
   float* os = vs + GS_GROUP * blockDim.x;      // [GROUP][threads]
   const bool col = c < vdim;
-  float* sp = a.state + (((size_t)a.state_slots[r] * a.heads + h) * dim) * vdim + c;
+  // where the walk starts from and where its last state goes
+  float* sp = a.mode == 0 ? a.state + (((size_t)a.state_slots[r] * a.heads + h) * dim) * vdim + c
+                          : a.z + (((size_t)blockIdx.y * a.heads + h) * dim) * vdim + c;
+  float* ap = os + GS_GROUP * blockDim.x;       // [DMAX]: launch A, the product of the block's gates
+  if (a.mode == 1) for (int i = threadIdx.x; i < DMAX; i += blockDim.x) ap[i] = 1.f;
   float S[DMAX];
 #pragma unroll
-  for (int i = 0; i < DMAX; ++i) S[i] = (col && i < dim) ? sp[(size_t)i * vdim] : 0.f;
+  for (int i = 0; i < DMAX; ++i) S[i] = (a.mode != 1 && col && i < dim) ? sp[(size_t)i * vdim] : 0.f;
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int g0 = t0; g0 < t1; g0 += GS_GROUP) {
     const int cnt = min(GS_GROUP, t1 - g0);
@@ -80,6 +118,12 @@ gated_scan_kernel(GatedScanArgs a) {
       vs[t * blockDim.x + e] = a.proj[(size_t)(g0 + t) * a.ld + a.v_col + h * vdim + c0 + e];
     }
     __syncthreads();
+    if (a.mode == 1)                            // each row's gates of this group into the block's product (a row has one owner)
+      for (int i = threadIdx.x; i < DMAX; i += blockDim.x) {
+        float pr = ap[i];
+        for (int t = 0; t < cnt; ++t) pr *= fs[t * DMAX + i];
+        ap[i] = pr;
+      }
     if (col) {
       for (int t = 0; t < cnt; ++t) {
         const float v = vs[t * blockDim.x + threadIdx.x];
@@ -98,7 +142,7 @@ gated_scan_kernel(GatedScanArgs a) {
       }
     }
     __syncthreads();
-    for (int t = warp; t < cnt; t += warps) {           // the head's norm, a warp per token
+    for (int t = warp; t < cnt && a.mode != 1; t += warps) {           // the head's norm, a warp per token
       const float* o = os + t * blockDim.x;
       if (a.raw) {                                      // the head has other slabs: its norm is the second kernel's
         float* dst = a.raw + ((size_t)(g0 + t) * a.heads + h) * vdim + c0;
@@ -113,11 +157,42 @@ gated_scan_kernel(GatedScanArgs a) {
     }
     __syncthreads();
   }
-  if (col) {
+  if (col && a.mode != 2) {
 #pragma unroll
     for (int i = 0; i < DMAX; ++i)
       if (i < dim) sp[(size_t)i * vdim] = S[i];
   }
+  if (a.mode == 1 && c0 == 0)
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) a.decay[((size_t)blockIdx.y * a.heads + h) * dim + i] = ap[i];
+}
+
+// Launch B: a thread per element (head, row, column) of a request's state carries it over the request's blocks.
+__global__ void __launch_bounds__(256)
+gated_scan_carry_kernel(GatedScanArgs a) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int r = blockIdx.y;
+  if (a.seq_lens[r] <= 0) return;
+  const size_t per = (size_t)a.heads * a.dim * a.vdim;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per) return;
+  int first = 0;                                   // index of the request's first block among all blocks
+  for (int i = 0; i < r; ++i) {
+    const int ql = a.seq_lens[i] > 0 ? a.cu_q[i + 1] - a.cu_q[i] : 0;
+    first += (ql + GS_BLOCK - 1) / GS_BLOCK;
+  }
+  const int blocks = (a.cu_q[r + 1] - a.cu_q[r] + GS_BLOCK - 1) / GS_BLOCK;
+  const size_t hi = e / a.vdim;                    // (head, row): the gate's index
+  float* slot = a.state + (size_t)a.state_slots[r] * per + e;
+  float S = *slot;
+#pragma unroll 4
+  for (int b = 0; b < blocks; ++b) {
+    float* zp = a.z + (size_t)(first + b) * per + e;
+    const float z = *zp, g = a.decay[(size_t)(first + b) * a.heads * a.dim + hi];
+    *zp = S;
+    S = fmaf(g, S, z);
+  }
+  *slot = S;
 }
 
 // out[t, h, :] = raw[t, h, :] / sqrt(mean(raw[t, h, :]^2) + eps) * w, a warp per (token, head).
@@ -148,19 +223,19 @@ static int gs_launch(GatedScanArgs a, int requests, int tokens, cudaStream_t s) 
   a.slabs = (a.vdim + threads - 1) / threads;
   if (a.slabs > 1 && !a.raw) return IFB_ERR_ARG;
   if (a.slabs == 1) a.raw = nullptr;
-  dim3 grid(a.heads * a.slabs, requests);
+  dim3 grid(a.heads * a.slabs, a.mode == 0 ? requests : (tokens + GS_BLOCK - 1) / GS_BLOCK + requests);
   int st = IFB_ERR_SIZE;
   bool done = false;
 #define GS_CASE(D)                                                                     \
   if (!done && a.dim <= D) {                                                           \
-    const size_t smem = (size_t)GS_GROUP * (2 * D + 2 * threads) * sizeof(float);      \
+    const size_t smem = ((size_t)GS_GROUP * (2 * D + 2 * threads) + D) * sizeof(float); \
     done = true;                                                                       \
     IFB_ALLOW_SMEM((gated_scan_kernel<T, D>), smem);                                   \
     st = ifb_launch(gated_scan_kernel<T, D>, grid, dim3(threads), smem, s, a);         \
   }
   GS_CASE(16) GS_CASE(32) GS_CASE(64) GS_CASE(128)
 #undef GS_CASE
-  if (st != IFB_OK || a.slabs == 1) return st;
+  if (st != IFB_OK || a.slabs == 1 || a.mode == 1) return st;
   const long long items = (long long)tokens * a.heads;
   return ifb_launch(head_norm_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, (const float*)a.raw, a.norm_w,
                     a.w_dtype, a.eps, (T*)a.out, items, a.vdim);
@@ -172,18 +247,41 @@ IFB_EXPORT int ifb_gated_scan_slabs(int dim, int vdim) {
   return (vdim + threads - 1) / threads;
 }
 
+// Floats of scratch (z, then decay) that the three-launch form needs for a step of these sizes.
+IFB_EXPORT long long ifb_gated_scan_scratch_floats(int tokens, int requests, int heads, int dim, int vdim) {
+  const long long blocks = (tokens + GS_BLOCK - 1) / GS_BLOCK + requests;
+  return blocks * heads * dim * ((long long)vdim + 1);
+}
+
+template <typename T>
+static int gs_run(GatedScanArgs a, int requests, int tokens, float* scratch, cudaStream_t s) {
+  if (!scratch) return gs_launch<T>(a, requests, tokens, s);
+  const long long blocks = (tokens + GS_BLOCK - 1) / GS_BLOCK + requests;
+  a.z = scratch;
+  a.decay = scratch + blocks * a.heads * a.dim * (long long)a.vdim;
+  a.mode = 1;
+  int st = gs_launch<T>(a, requests, tokens, s);
+  if (st != IFB_OK) return st;
+  const size_t per = (size_t)a.heads * a.dim * a.vdim;
+  st = ifb_launch(gated_scan_carry_kernel, dim3((unsigned)((per + 255) / 256), requests), dim3(256), 0, s, a);
+  if (st != IFB_OK) return st;
+  a.mode = 2;
+  return gs_launch<T>(a, requests, tokens, s);
+}
+
 // dim up to 128, any vdim.  bias, lower and norm_w share one dtype.  raw: float32 [tokens][heads * vdim] scratch, needed
-// when ifb_gated_scan_slabs(dim, vdim) > 1.
+// when ifb_gated_scan_slabs(dim, vdim) > 1.  scratch: null for the one-launch walk (a request per block row); else
+// ifb_gated_scan_scratch_floats(...) floats for the three-launch form, in which blocks of 64 tokens run side by side.
 IFB_EXPORT int ifb_gated_scan(const float* proj, int ld, int q_col, int f_col, int v_col, const void* bias, const void* lower,
                               const void* norm_w, int w_dtype, float eps, float* state, const int* state_slots, const int* cu_q,
-                              const int* seq_lens, void* out, int out_dtype, float* raw, int requests, int tokens, int heads,
-                              int dim, int vdim, cudaStream_t stream) {
+                              const int* seq_lens, void* out, int out_dtype, float* raw, float* scratch, int requests, int tokens,
+                              int heads, int dim, int vdim, cudaStream_t stream) {
   if (requests <= 0 || tokens <= 0) return IFB_OK;
   if (heads < 1 || dim < 1 || vdim < 1 || dim > 128 || requests > 65535) return IFB_ERR_SIZE;
   if (w_dtype != IFB_F32 && w_dtype != IFB_BF16) return IFB_ERR_DTYPE;
   GatedScanArgs a{proj, ld, q_col, f_col, v_col, bias, lower, norm_w, w_dtype, eps, state, state_slots, cu_q, seq_lens, out,
-                  raw, heads, dim, vdim, 1};
-  if (out_dtype == IFB_F32) return gs_launch<float>(a, requests, tokens, stream);
-  if (out_dtype == IFB_BF16) return gs_launch<__nv_bfloat16>(a, requests, tokens, stream);
+                  raw, heads, dim, vdim, 1, 0, requests, nullptr, nullptr};
+  if (out_dtype == IFB_F32) return gs_run<float>(a, requests, tokens, scratch, stream);
+  if (out_dtype == IFB_BF16) return gs_run<__nv_bfloat16>(a, requests, tokens, scratch, stream);
   return IFB_ERR_DTYPE;
 }

@@ -36,7 +36,7 @@ LIBRARIES: Dict[str, tuple] = {
     "linear_skinny_static": (["linear_skinny_static.cu"], []),
     "attention_tc": (["attention_tc.cu"], []),            # head size 128
     # post-norm sublayers (embedding with a position vector, residual update), the gated recurrence, talking attention
-    "mixers": (["sublayer.cu", "gated_scan.cu", "attention_talk.cu"], []),
+    "mixers": (["sublayer.cu", "gated_scan.cu", "attention_talk.cu", "attention_talk_mma.cu"], []),
     # compiled once per head size: defines={"HEAD_DIM": d}
     "attention_mma": (["attention_mma.cu"], []),
 }

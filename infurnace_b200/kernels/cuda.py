@@ -105,6 +105,11 @@ class CudaKernels:
         # up to here norms are folded into products (the kernels take 64 rows; beyond 32 the separate norm measured faster)
         self.fold_max_rows = int(os.environ.get("INFURNACE_FOLD_MAX_ROWS", "32"))
         self.split_min_keys = int(os.environ.get("INFURNACE_SPLIT_MIN_KEYS", "256"))   # fewest keys a split of a context gets
+        self.talk_mma = os.environ.get("INFURNACE_TALK_MMA", "1") != "0"    # talking attention on tensor cores where it fits
+        self.talk_mma_calls = 0
+        self.scan_block_min = int(os.environ.get("INFURNACE_SCAN_BLOCK_MIN", "97"))     # tokens of the longest request from
+        self.scan_blocked_calls = 0                                                    # which the recurrence runs in blocks
+        self._scan_scratch = None
         self._mix = None               # the library of post-norm sublayers, the gated recurrence and talking attention
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
         # device int: non-zero after a kernel recorded a fault it contained (a bounded barrier wait that gave up, a
@@ -651,11 +656,17 @@ class CudaKernels:
                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
             m.ifb_gated_scan_slabs.argtypes = [c_int, c_int]
             m.ifb_gated_scan.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float,
-                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                         c_int, c_int, c_void_p]
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                         c_int, c_int, c_int, c_int, c_void_p]
+            m.ifb_gated_scan_scratch_floats.restype = c_longlong
+            m.ifb_gated_scan_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
             m.ifb_attention_talk.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                              c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                              c_float, c_float, c_void_p]
+            m.ifb_attention_talk_mma_fits.argtypes = [c_int, c_int, c_int]
+            m.ifb_attention_talk_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                 c_float, c_float, c_void_p]
         return self._mix
 
     def embed_sinusoid(self, table, ids, positions, inv_freq, out, half=None):
@@ -731,11 +742,13 @@ class CudaKernels:
         return int(self._mix_lib().ifb_gated_scan_slabs(int(dim), int(vdim)))
 
     def gated_scan(self, proj, q_col, f_col, v_col, bias, lower, norm_weight, eps, state, state_slots, cu_q, seq_lens, out,
-                   heads, dim, vdim, raw=None):
+                   heads, dim, vdim, raw=None, max_q_len=1):
         """The gated linear recurrence over this step's tokens of every request (csrc/gated_scan.cu): proj [n, ld]
         float32 holds q_raw, f_raw (heads * dim each) and v (heads * vdim) at the given columns; state
         [slots, heads, dim, vdim] float32 is read and written at each request's slot; out [n, heads * vdim] gets the
-        normalised outputs.  A request with seq_lens 0 is padding: its state is left alone."""
+        normalised outputs.  A request with seq_lens 0 is padding: its state is left alone.  ``max_q_len``: the most
+        tokens a request brings; from ``scan_block_min`` on, the requests are cut into blocks of 64 tokens that run
+        side by side (three launches), which differs from the one-launch walk by rounding only."""
         _dense(proj, "proj", torch.float32), _dense(state, "state", torch.float32), _dense(out, "out")
         _dense(state_slots, "state_slots", torch.int32), _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
         n, ld = proj.shape
@@ -750,11 +763,19 @@ class CudaKernels:
             raise KernelError("gated_scan: sizes of proj, state, out and the request arrays do not match")
         if raw is not None and (_dense(raw, "raw", torch.float32).shape != (n, hv)):
             raise KernelError("gated_scan: raw is float32 [tokens, heads * vdim]")
-        self.launches += 1 if raw is None or self.gated_scan_slabs(dim, vdim) == 1 else 2
+        scratch = None
+        if max_q_len >= self.scan_block_min:
+            need = int(self._mix_lib().ifb_gated_scan_scratch_floats(n, r, heads, dim, vdim))
+            if self._scan_scratch is None or self._scan_scratch.numel() < need:
+                self._scan_scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+                self.scratch_generation += 1
+            scratch = self._scan_scratch
+            self.scan_blocked_calls += 1
+        self.launches += (1 if scratch is None else 3) + (0 if raw is None or self.gated_scan_slabs(dim, vdim) == 1 else 1)
         _check(self._mix_lib().ifb_gated_scan(
             proj.data_ptr(), ld, int(q_col), int(f_col), int(v_col), bias.data_ptr(), lower.data_ptr(), norm_weight.data_ptr(),
             _code(bias), float(eps), state.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(),
-            out.data_ptr(), _code(out), _ptr(raw), r, n, heads, dim, vdim, self._stream()), "gated_scan")
+            out.data_ptr(), _code(out), _ptr(raw), _ptr(scratch), r, n, heads, dim, vdim, self._stream()), "gated_scan")
 
     def attention_talk(self, q, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
                        chunk=0, slope_exponent=0.0, talk=None, gate=None, gate_col=0, max_q_len=0):
@@ -781,6 +802,15 @@ class CudaKernels:
                 raise KernelError("attention_talk: gate has a row per token and heads * head_dim columns from gate_col")
             gate_ptr, gate_ld = gate.data_ptr() + 4 * int(gate_col), gate.shape[1]
         self.launches += 1
+        if self.talk_mma and q.dtype == torch.bfloat16 and self._mix_lib().ifb_attention_talk_mma_fits(num_heads, num_kv_heads,
+                                                                                                       head_dim):
+            # bfloat16 on the tensor cores (csrc/attention_talk_mma.cu); other sizes and float32 run the plain kernel
+            self.talk_mma_calls += 1
+            return _check(self._mix_lib().ifb_attention_talk_mma(
+                q.data_ptr(), kv_pages.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), cu_q.data_ptr(),
+                seq_lens.data_ptr(), _ptr(talk), _code(talk) if talk is not None else 0, gate_ptr, gate_ld, out.data_ptr(), n, r,
+                num_heads, num_kv_heads, head_dim, kv_pages.shape[3], int(chunk or 0), float(scale),
+                float(slope_exponent or 0.0), self._stream()), "attention_talk")
         _check(self._mix_lib().ifb_attention_talk(
             q.data_ptr(), _code(q), kv_pages.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), cu_q.data_ptr(),
             seq_lens.data_ptr(), _ptr(talk), _code(talk) if talk is not None else 0, gate_ptr, gate_ld, out.data_ptr(), n, r,

@@ -38,7 +38,8 @@ class GatedRecurrence:
         out = ctx.buffer("gr_out", (n, self.hv), self.rt.act_dtype)
         raw = ctx.buffer("gr_raw", (n, self.hv), torch.float32) if self.slabs > 1 else None
         k.gated_scan(proj, 0, self.hd, 2 * self.hd, self.bias, self.lower, self.norm_w, s.eps, ctx.state(call.cache),
-                     ctx.state_slots, ctx.cu_q, ctx.seq_lens, out, s.num_heads, s.head_dim, s.value_head_dim, raw=raw)
+                     ctx.state_slots, ctx.cu_q, ctx.seq_lens, out, s.num_heads, s.head_dim, s.value_head_dim, raw=raw,
+                     max_q_len=ctx.max_q_len)
         delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
         k.linear(out, self.w_o, delta)
         return delta

@@ -238,7 +238,7 @@ class ReferenceKernels:
         return 1
 
     def gated_scan(self, proj, q_col, f_col, v_col, bias, lower, norm_weight, eps, state, state_slots, cu_q, seq_lens, out,
-                   heads, dim, vdim, raw=None):
+                   heads, dim, vdim, raw=None, max_q_len=1):
         """Token by token for each request r (rows cu_q[r] .. cu_q[r+1]-1; seq_lens[r] == 0: padding, skipped), on the
         state rows state[state_slots[r]]: S = f[:, None] * S + (1 - f)[:, None] * v[None, :], o = S^T q, with
         q = silu(q_raw), f = lower + (1 - lower) * sigmoid(f_raw + bias); out = o / rms(o) * norm_weight per head."""

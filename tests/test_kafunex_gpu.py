@@ -107,14 +107,14 @@ def _scan_inputs(heads, dim, vdim, n, seed):
 def test_gated_recurrence_kernel(K, heads, dim, vdim):
     """Unequal requests in one call (one of them padding), states that are not zero, and the same tokens cut into
     a prompt, a portion and single tokens: the state carries everything."""
-    lens = [37, 1, 5, 0, 18]                                   # the fourth is padding: one row, length 0
-    cu = [0, 37, 38, 43, 44, 62]
+    lens = [37, 1, 5, 0, 18, 200]                              # the fourth is padding: one row, length 0
+    cu = [0, 37, 38, 43, 44, 62, 262]
     n, hd, hv = cu[-1], heads * dim, heads * vdim
     proj, bias, lower, nw = _scan_inputs(heads, dim, vdim, n, heads + dim + vdim)
-    slots = torch.tensor([2, 0, 5, 0, 3], dtype=torch.int32)
-    state0 = torch.randn(6, heads, dim, vdim, generator=gen(1))
+    slots = torch.tensor([2, 0, 5, 0, 3, 6], dtype=torch.int32)
+    state0 = torch.randn(7, heads, dim, vdim, generator=gen(1))
     want_state, want = state0.clone().double(), torch.zeros(n, hv, dtype=torch.float64)
-    seq = torch.tensor([100, 1, 9, 0, 18], dtype=torch.int32)
+    seq = torch.tensor([100, 1, 9, 0, 18, 333], dtype=torch.int32)
     REF.gated_scan(proj, 0, hd, 2 * hd, bias, lower, nw, 1e-5, want_state, slots, torch.tensor(cu, dtype=torch.int32), seq, want,
                    heads, dim, vdim)
     raw = torch.zeros(n, hv, device="cuda") if K.gated_scan_slabs(dim, vdim) > 1 else None
@@ -137,6 +137,12 @@ def test_gated_recurrence_kernel(K, heads, dim, vdim):
                      raw=raw[:count] if raw is not None else None)
         start += count
     close(got2, want[:37], 2e-5, "outputs of the cut request"), close(state2[2], want_state[2], 2e-5, "its state")
+    # the same step with the requests cut into blocks that run side by side
+    state3, got3, before = state0.cuda(), torch.zeros(n, hv, device="cuda"), K.scan_blocked_calls
+    K.gated_scan(proj.cuda(), 0, hd, 2 * hd, bias.cuda(), lower.cuda(), nw.cuda(), 1e-5, state3, slots.cuda(),
+                 torch.tensor(cu, dtype=torch.int32).cuda(), seq.cuda(), got3, heads, dim, vdim, raw=raw, max_q_len=1000)
+    assert K.scan_blocked_calls == before + 1
+    close(got3[rows], want[rows], 2e-5, "outputs in blocks"), close(state3, want_state, 2e-5, "states in blocks")
     out_bf = torch.zeros(n, hv, device="cuda", dtype=torch.bfloat16)
     K.gated_scan(proj.cuda(), 0, hd, 2 * hd, bias.cuda(), lower.cuda(), nw.cuda(), 1e-5, state0.cuda(), slots.cuda(),
                  torch.tensor(cu, dtype=torch.int32).cuda(), seq.cuda(), out_bf, heads, dim, vdim, raw=raw)
@@ -195,8 +201,10 @@ def test_talking_attention_kernel(K, H, G, d, ps, chunk, dtype):
     and after a chunk's edge, and a padding row."""
     c = chunk or 50
     cases = [(70, 70), (c + 1, 1), (c, 1), (2 * c - 1, 1), (2 * c + 5, c + 3), (1, 1), (3 * c + 2, 2), (0, 1), (210, 1)]
+    before = K.talk_mma_calls
     got, want = _attention_case(K, H, G, d, ps, chunk, dtype, cases, seed=H * d + chunk)
     close(got, want, 2e-5 if dtype == torch.float32 else 0.06, "attention")
+    assert (K.talk_mma_calls > before) == (dtype == torch.bfloat16 and d in (16, 32, 64, 128))      # which kernel ran
 
 
 def test_talking_attention_variants(K):
@@ -205,14 +213,18 @@ def test_talking_attention_variants(K):
         close(got, want, 2e-5, str(kw))
 
 
-def test_a_far_key_and_the_keys_at_a_chunks_edge(K):
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_far_key_and_the_keys_at_a_chunks_edge(K, dtype):
     """One key among hundreds holds nearly all the weight of the last query: inside the chunk it must be found (its
-    value is 9 everywhere), one position before the chunk's first it must not be seen."""
+    value is 9 everywhere), one position before the chunk's first it must not be seen; as a decoded token and as the
+    last token of a portion that straddles the chunk's edge."""
     for key_pos, seen in ((400, True), (399, False), (1099, True)):
-        got, want = _attention_case(K, 4, 4, 16, 16, 400, torch.float32, [(1100, 1)] if key_pos > 1000 else [(790, 1)], seed=11,
-                                    talk=False, gate=False, slope=0.0, plant=(key_pos, 400.0))
-        close(got, want, 2e-5, f"planted key at {key_pos}")
-        assert (float(got.abs().min()) > 8.9) == seen, key_pos
+        for new in (1, 23, 395):
+            L = 1100 if key_pos > 1000 else 790
+            got, want = _attention_case(K, 4, 4, 16, 16, 400, dtype, [(L, new)], seed=11, talk=False, gate=False, slope=0.0,
+                                        plant=(key_pos, 400.0))
+            close(got, want, 2e-5 if dtype == torch.float32 else 0.08, f"planted key at {key_pos}, portion of {new}")
+            assert (float(got[-1].float().abs().min()) > 8.9) == seen, (key_pos, new)
 
 
 @pytest.mark.parametrize("epilogue", ["relu2", "silu", "sigmoid", "gelu_tanh"])

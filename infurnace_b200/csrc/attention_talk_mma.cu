@@ -13,6 +13,9 @@
 // With more query heads than NW the groups are CTAs of their own, each of which forms the raw scores again (tensor
 // work that is cheap beside step 3, whose cost does not depend on the split).  The output is multiplied by
 // sigmoid(gate) and stored as bfloat16.  Head sizes 16, 32, 64, 128.
+// A step of few query tokens (decoding) has few tiles; its keys are then split over several CTAs per tile (each takes
+// every splits-th tile of 32 keys; the mixing is per (query, key) pair, so any split of the keys is exact), and a
+// second kernel merges the parts in a fixed order.
 #include "common.cuh"
 #include <math.h>
 #include <mma.h>
@@ -33,6 +36,8 @@ struct TalkMmaArgs {
   bf16* out;                // [tokens][H * D]
   int n_tokens, n_req, H, G, page_size, chunk;
   float scale, slope_exp;
+  int splits;               // > 1: CTA z takes every splits-th tile of keys and leaves its part in `parts` for the merge
+  float* parts;             // [tokens][H][splits][D + 2]: the unnormalised output row, then the maximum and the sum
 };
 
 constexpr int TM_ROWS = 16, TM_KEYS = 32;
@@ -126,7 +131,7 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
   for (int n = 0; n < D / 8; ++n) { O[n][0] = O[n][1] = O[n][2] = O[n][3] = 0.f; }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-  for (int k0 = first; k0 <= p_last; k0 += TM_KEYS) {
+  for (int k0 = first + (int)blockIdx.z * TM_KEYS; k0 <= p_last; k0 += TM_KEYS * a.splits) {
     // ---- 1. keys and values of this tile
     for (int idx = tid; idx < (G + GV) * TM_KEYS * CH; idx += NW * 32) {
       const int c = idx % CH, j = (idx / CH) % TM_KEYS, gg = idx / (CH * TM_KEYS);
@@ -178,19 +183,23 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
     // ---- 3. the heads' scores of each (query, key) pair mixed, for the group's heads
     const float* Sc = Ss + (size_t)o0 * TM_ROWS * TM_KEYS;          // without mixing: the group's own scores
     if (a.talk) {
-      for (int pair = tid; pair < TM_ROWS * TM_KEYS; pair += NW * 32) {
-        float b[NW];
+      // a thread takes four neighbouring keys of one query and four heads of the group: per source head one 16-byte
+      // load of scores, one of weights (the same for the whole warp) and sixteen multiply-adds
+      const int pq = tid & 127, oq = tid >> 7;            // 128 quads of pairs x NW / 4 quads of heads = the block
+      float b[4][4];
 #pragma unroll
-        for (int o = 0; o < NW; ++o) b[o] = 0.f;
-        for (int h = 0; h < H; ++h) {
-          const float s = Ss[(size_t)h * TM_ROWS * TM_KEYS + pair];
-          const float* t = Tt + h * NW;
-#pragma unroll
-          for (int o = 0; o < NW; ++o) b[o] = fmaf(t[o], s, b[o]);
-        }
-#pragma unroll
-        for (int o = 0; o < NW; ++o) Ms[o * TM_ROWS * TM_KEYS + pair] = b[o];
+      for (int o = 0; o < 4; ++o) { b[o][0] = b[o][1] = b[o][2] = b[o][3] = 0.f; }
+      for (int h = 0; h < H; ++h) {
+        const float4 s4 = *reinterpret_cast<const float4*>(Ss + (size_t)h * TM_ROWS * TM_KEYS + pq * 4);
+        const float4 t4 = *reinterpret_cast<const float4*>(Tt + h * NW + oq * 4);
+        b[0][0] = fmaf(t4.x, s4.x, b[0][0]); b[0][1] = fmaf(t4.x, s4.y, b[0][1]); b[0][2] = fmaf(t4.x, s4.z, b[0][2]); b[0][3] = fmaf(t4.x, s4.w, b[0][3]);
+        b[1][0] = fmaf(t4.y, s4.x, b[1][0]); b[1][1] = fmaf(t4.y, s4.y, b[1][1]); b[1][2] = fmaf(t4.y, s4.z, b[1][2]); b[1][3] = fmaf(t4.y, s4.w, b[1][3]);
+        b[2][0] = fmaf(t4.z, s4.x, b[2][0]); b[2][1] = fmaf(t4.z, s4.y, b[2][1]); b[2][2] = fmaf(t4.z, s4.z, b[2][2]); b[2][3] = fmaf(t4.z, s4.w, b[2][3]);
+        b[3][0] = fmaf(t4.w, s4.x, b[3][0]); b[3][1] = fmaf(t4.w, s4.y, b[3][1]); b[3][2] = fmaf(t4.w, s4.z, b[3][2]); b[3][3] = fmaf(t4.w, s4.w, b[3][3]);
       }
+#pragma unroll
+      for (int o = 0; o < 4; ++o)
+        *reinterpret_cast<float4*>(Ms + (size_t)(oq * 4 + o) * TM_ROWS * TM_KEYS + pq * 4) = make_float4(b[o][0], b[o][1], b[o][2], b[o][3]);
       __syncthreads();
       Sc = Ms;
     }
@@ -215,13 +224,13 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
       const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
       const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;     // a row that has seen no key yet
-      const float c0 = expf(m0 - b0), c1 = expf(m1 - b1);
+      const float c0 = __expf(m0 - b0), c1 = __expf(m1 - b1);      // P is rounded to bfloat16 below: ex2's error is far under that
       m0 = n0; m1 = n1;
       float sum0 = 0.f, sum1 = 0.f;
       uint32_t pa[2][4];
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
-        const float e0 = expf(s[n][0] - b0), e1 = expf(s[n][1] - b0), e2 = expf(s[n][2] - b1), e3 = expf(s[n][3] - b1);
+        const float e0 = __expf(s[n][0] - b0), e1 = __expf(s[n][1] - b0), e2 = __expf(s[n][2] - b1), e3 = __expf(s[n][3] - b1);
         sum0 += e0 + e1; sum1 += e2 + e3;
         pa[n >> 1][(n & 1) * 2] = tm_pack(e0, e1);
         pa[n >> 1][(n & 1) * 2 + 1] = tm_pack(e2, e3);
@@ -245,9 +254,24 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
     }
     __syncthreads();
   }
+  tm_cp_wait();                             // a CTA without a tile of keys has the copies of its queries in flight
   if (warp >= heads_here) return;
-  const float i0 = 1.f / l0, i1 = 1.f / l1;
   const int head = o0 + warp;
+  if (a.splits > 1) {                       // this CTA's part: rows as they are, with their maxima and sums
+    float* pr0p = a.parts + (((size_t)(q0 + rl) * H + head) * a.splits + blockIdx.z) * (D + 2);
+    float* pr1p = a.parts + (((size_t)(q0 + rl + 8) * H + head) * a.splits + blockIdx.z) * (D + 2);
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      if (row0) *reinterpret_cast<float2*>(pr0p + n * 8 + cl) = make_float2(O[n][0], O[n][1]);
+      if (row1) *reinterpret_cast<float2*>(pr1p + n * 8 + cl) = make_float2(O[n][2], O[n][3]);
+    }
+    if ((lane & 3) == 0) {
+      if (row0) { pr0p[D] = m0; pr0p[D + 1] = l0; }
+      if (row1) { pr1p[D] = m1; pr1p[D + 1] = l1; }
+    }
+    return;
+  }
+  const float i0 = 1.f / l0, i1 = 1.f / l1;
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) {
     const int col = head * D + n * 8 + cl;
@@ -267,6 +291,48 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
       }
       *reinterpret_cast<uint32_t*>(a.out + (size_t)(q0 + rl + 8) * H * D + col) = tm_pack(x, y);
     }
+  }
+}
+
+// out[t, h, :] = sum_z parts[t, h, z, :D] * exp(m_z - m) / sum_z l_z * exp(m_z - m), m = max_z m_z, times sigmoid(gate):
+// a warp per (token, head), the parts added in ascending z.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_talk_merge_kernel(TalkMmaArgs a) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= (long long)a.n_tokens * a.H) return;
+  const int tok = (int)(item / a.H), h = (int)(item % a.H);
+  // a padding row (no request behind it) has no parts: its output is zero
+  int lo = 0, hi = a.n_req;
+  while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (a.cu_q[mid] <= tok) lo = mid; else hi = mid; }
+  const bool live = tok < a.cu_q[a.n_req] && a.seq_lens[lo] > 0;
+  const float* p = a.parts + (size_t)item * a.splits * (D + 2);
+  float m = -INFINITY;
+  if (live) for (int z = 0; z < a.splits; ++z) m = fmaxf(m, p[(size_t)z * (D + 2) + D]);
+  constexpr int PER = (D + 31) / 32;
+  float acc[PER], l = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) acc[j] = 0.f;
+  if (live)
+    for (int z = 0; z < a.splits; ++z) {
+      const float* pz = p + (size_t)z * (D + 2);
+      const float mz = pz[D];
+      if (mz == -INFINITY) continue;               // a split that saw no key
+      const float w = expf(mz - m);
+      l += pz[D + 1] * w;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) { const int c = lane + 32 * j; if (c < D) acc[j] = fmaf(pz[c], w, acc[j]); }
+    }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int c = lane + 32 * j;
+    if (c >= D) continue;
+    float o = live ? acc[j] / l : 0.f;
+    if (live && a.gate) o *= 1.f / (1.f + expf(-a.gate[(size_t)tok * a.gate_ld + h * D + c]));
+    a.out[(size_t)tok * a.H * D + h * D + c] = __float2bfloat16_rn(o);
   }
 }
 
@@ -298,8 +364,11 @@ static int tm_launch(const TalkMmaArgs& a, cudaStream_t s) {
   const int gv_max = tm_gv_max(a.H, a.G, NW);
   const size_t smem = tm_smem_bytes(a.H, a.G, D, NW, gv_max);
   IFB_ALLOW_SMEM((attention_talk_mma_kernel<D, NW>), smem);
-  dim3 grid((a.n_tokens + TM_ROWS - 1) / TM_ROWS + a.n_req, (a.H + NW - 1) / NW);
-  return ifb_launch(attention_talk_mma_kernel<D, NW>, grid, dim3(NW * 32), smem, s, a, gv_max);
+  dim3 grid((a.n_tokens + TM_ROWS - 1) / TM_ROWS + a.n_req, (a.H + NW - 1) / NW, a.splits);
+  const int st = ifb_launch(attention_talk_mma_kernel<D, NW>, grid, dim3(NW * 32), smem, s, a, gv_max);
+  if (st != IFB_OK || a.splits == 1) return st;
+  const long long items = (long long)a.n_tokens * a.H;
+  return ifb_launch(attention_talk_merge_kernel<D>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, a);
 }
 
 template <int D>
@@ -311,18 +380,19 @@ static int tm_by_heads(const TalkMmaArgs& a, cudaStream_t s) {
   }
 }
 
+// splits > 1 needs parts: n_tokens * H * splits * (d + 2) floats.
 IFB_EXPORT int ifb_attention_talk_mma(const void* q, const void* pages, const int* block_tables, int bt_stride, const int* cu_q,
                                       const int* seq_lens, const void* talk, int talk_dtype, const float* gate, int gate_ld,
                                       void* out, int n_tokens, int n_req, int H, int G, int d, int page_size, int chunk,
-                                      float scale, float slope_exp, cudaStream_t stream) {
+                                      float scale, float slope_exp, int splits, float* parts, cudaStream_t stream) {
   if (n_tokens <= 0 || n_req <= 0) return IFB_OK;
   if (!ifb_attention_talk_mma_fits(H, G, d)) return IFB_ERR_SIZE;
-  if (page_size < 1 || chunk < 0) return IFB_ERR_ARG;
+  if (page_size < 1 || chunk < 0 || splits < 1 || splits > 64 || (splits > 1 && !parts)) return IFB_ERR_ARG;
   if (((uintptr_t)q & 15) || ((uintptr_t)pages & 15) || ((uintptr_t)out & 3)) return IFB_ERR_ALIGN;
   if (gate && ((uintptr_t)gate & 3)) return IFB_ERR_ALIGN;
   if (talk && talk_dtype != IFB_F32 && talk_dtype != IFB_BF16) return IFB_ERR_DTYPE;
   TalkMmaArgs a{(const bf16*)q, (const bf16*)pages, block_tables, bt_stride, cu_q, seq_lens, talk, talk_dtype, gate, gate_ld,
-                (bf16*)out, n_tokens, n_req, H, G, page_size, chunk, scale, slope_exp};
+                (bf16*)out, n_tokens, n_req, H, G, page_size, chunk, scale, slope_exp, splits, parts};
   switch (d) {
     case 16: return tm_by_heads<16>(a, stream);
     case 32: return tm_by_heads<32>(a, stream);

@@ -96,28 +96,72 @@ gated_scan_kernel(GatedScanArgs a) {
 #pragma unroll
   for (int i = 0; i < DMAX; ++i) S[i] = (a.mode != 1 && col && i < dim) ? sp[(size_t)i * vdim] : 0.f;
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // With rows of 33 to 64 (the usual head) a block of at least 128 threads asks for the next group's numbers while it
+  // walks the present one: the walk is a chain per thread, and with few warps on an SM nothing else hides the loads.
+  constexpr bool AHEAD = DMAX == 64;
+  constexpr int QF = AHEAD ? GS_GROUP * DMAX / 128 : 1;
+  float nq[QF], nf[QF], nv[AHEAD ? GS_GROUP : 1];
+  const bool ahead = AHEAD && blockDim.x >= 128;
+  auto fetch = [&](int g0) {
+    const int cnt = min(GS_GROUP, t1 - g0);
+#pragma unroll
+    for (int j = 0; j < QF; ++j) {
+      const int idx = threadIdx.x + j * blockDim.x, t = idx / DMAX, i = idx % DMAX;
+      nq[j] = nf[j] = 0.f;
+      if (idx < cnt * DMAX && i < dim) {
+        const float* row = a.proj + (size_t)(g0 + t) * a.ld;
+        nq[j] = row[a.q_col + h * dim + i];
+        nf[j] = row[a.f_col + h * dim + i];
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < (AHEAD ? GS_GROUP : 1); ++t)
+      nv[t] = (t < cnt && col) ? a.proj[(size_t)(g0 + t) * a.ld + a.v_col + h * vdim + c] : 0.f;
+  };
+  if (ahead) fetch(t0);
   for (int g0 = t0; g0 < t1; g0 += GS_GROUP) {
     const int cnt = min(GS_GROUP, t1 - g0);
     // rows dim .. DMAX-1 are padding: f = 1 keeps their (zero) entries, q = 0 keeps them out of the sums
-    for (int idx = threadIdx.x; idx < cnt * DMAX; idx += blockDim.x) {
-      const int t = idx / DMAX, i = idx % DMAX;
-      float qv = 0.f, fv = 1.f;
-      if (i < dim) {
-        const float* row = a.proj + (size_t)(g0 + t) * a.ld;
-        const float qr = row[a.q_col + h * dim + i];
-        qv = qr / (1.f + expf(-qr));
-        const float lo = load_as_f32(a.lower, a.w_dtype, h * dim + i);
-        const float z = row[a.f_col + h * dim + i] + load_as_f32(a.bias, a.w_dtype, h * dim + i);
-        fv = lo + (1.f - lo) * (1.f / (1.f + expf(-z)));
+    if (ahead) {
+#pragma unroll
+      for (int j = 0; j < QF; ++j) {
+        const int idx = threadIdx.x + j * blockDim.x, i = idx % DMAX;
+        if (idx >= cnt * DMAX) continue;
+        float qv = 0.f, fv = 1.f;
+        if (i < dim) {
+          qv = nq[j] / (1.f + expf(-nq[j]));
+          const float lo = load_as_f32(a.lower, a.w_dtype, h * dim + i);
+          const float z = nf[j] + load_as_f32(a.bias, a.w_dtype, h * dim + i);
+          fv = lo + (1.f - lo) * (1.f / (1.f + expf(-z)));
+        }
+        qs[idx] = qv;
+        fs[idx] = fv;
       }
-      qs[idx] = qv;
-      fs[idx] = fv;
-    }
-    for (int idx = threadIdx.x; idx < cnt * width; idx += blockDim.x) {
-      const int t = idx / width, e = idx % width;
-      vs[t * blockDim.x + e] = a.proj[(size_t)(g0 + t) * a.ld + a.v_col + h * vdim + c0 + e];
+#pragma unroll
+      for (int t = 0; t < (AHEAD ? GS_GROUP : 1); ++t)
+        if (t < cnt) vs[t * blockDim.x + threadIdx.x] = nv[t];
+    } else {
+      for (int idx = threadIdx.x; idx < cnt * DMAX; idx += blockDim.x) {
+        const int t = idx / DMAX, i = idx % DMAX;
+        float qv = 0.f, fv = 1.f;
+        if (i < dim) {
+          const float* row = a.proj + (size_t)(g0 + t) * a.ld;
+          const float qr = row[a.q_col + h * dim + i];
+          qv = qr / (1.f + expf(-qr));
+          const float lo = load_as_f32(a.lower, a.w_dtype, h * dim + i);
+          const float z = row[a.f_col + h * dim + i] + load_as_f32(a.bias, a.w_dtype, h * dim + i);
+          fv = lo + (1.f - lo) * (1.f / (1.f + expf(-z)));
+        }
+        qs[idx] = qv;
+        fs[idx] = fv;
+      }
+      for (int idx = threadIdx.x; idx < cnt * width; idx += blockDim.x) {
+        const int t = idx / width, e = idx % width;
+        vs[t * blockDim.x + e] = a.proj[(size_t)(g0 + t) * a.ld + a.v_col + h * vdim + c0 + e];
+      }
     }
     __syncthreads();
+    if (ahead && g0 + GS_GROUP < t1) fetch(g0 + GS_GROUP);
     if (a.mode == 1)                            // each row's gates of this group into the block's product (a row has one owner)
       for (int i = threadIdx.x; i < DMAX; i += blockDim.x) {
         float pr = ap[i];

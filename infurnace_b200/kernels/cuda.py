@@ -107,6 +107,7 @@ class CudaKernels:
         self.split_min_keys = int(os.environ.get("INFURNACE_SPLIT_MIN_KEYS", "256"))   # fewest keys a split of a context gets
         self.talk_mma = os.environ.get("INFURNACE_TALK_MMA", "1") != "0"    # talking attention on tensor cores where it fits
         self.talk_mma_calls = 0
+        self.talk_split_calls = 0      # of these, with the keys of a tile split over several CTAs
         self.scan_block_min = int(os.environ.get("INFURNACE_SCAN_BLOCK_MIN", "97"))     # tokens of the longest request from
         self.scan_blocked_calls = 0                                                    # which the recurrence runs in blocks
         self._scan_scratch = None
@@ -666,7 +667,7 @@ class CudaKernels:
             m.ifb_attention_talk_mma_fits.argtypes = [c_int, c_int, c_int]
             m.ifb_attention_talk_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                  c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                 c_float, c_float, c_void_p]
+                                                 c_float, c_float, c_int, c_void_p, c_void_p]
         return self._mix
 
     def embed_sinusoid(self, table, ids, positions, inv_freq, out, half=None):
@@ -778,11 +779,14 @@ class CudaKernels:
             out.data_ptr(), _code(out), _ptr(raw), _ptr(scratch), r, n, heads, dim, vdim, self._stream()), "gated_scan")
 
     def attention_talk(self, q, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
-                       chunk=0, slope_exponent=0.0, talk=None, gate=None, gate_col=0, max_q_len=0):
+                       chunk=0, slope_exponent=0.0, talk=None, gate=None, gate_col=0, max_q_len=0, max_seq_len=0):
         """Attention over the pages with the heads' scores mixed before the softmax (csrc/attention_talk.cu).
         q [n, heads * head_dim]: the queries, already normalised.  ``chunk`` 0: every earlier key is visible.
         ``slope_exponent`` 0: no distance bias.  ``talk`` [heads, heads] or None.  ``gate``: a float32 matrix whose
-        columns gate_col .. gate_col + heads * head_dim hold the gate before its sigmoid, or None."""
+        columns gate_col .. gate_col + heads * head_dim hold the gate before its sigmoid, or None.  ``max_q_len`` and
+        ``max_seq_len`` (the most tokens a request brings, and an upper bound of the longest request after the step; 0:
+        unknown) only decide how the work is spread: a step of few tokens over long contexts has its keys split
+        over several CTAs."""
         _dense(q, "q"), _dense(kv_pages, "kv_pages", q.dtype), _dense(out, "out", q.dtype)
         _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
         if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
@@ -806,16 +810,35 @@ class CudaKernels:
                                                                                                        head_dim):
             # bfloat16 on the tensor cores (csrc/attention_talk_mma.cu); other sizes and float32 run the plain kernel
             self.talk_mma_calls += 1
+            splits, parts = self._talk_splits(n, r, num_heads, head_dim, int(chunk or 0), max_q_len, max_seq_len), None
+            if splits > 1:
+                parts = self.attention_scratch(n * num_heads * splits * (head_dim + 2))
+                self.launches += 1
+                self.talk_split_calls += 1
             return _check(self._mix_lib().ifb_attention_talk_mma(
                 q.data_ptr(), kv_pages.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), cu_q.data_ptr(),
                 seq_lens.data_ptr(), _ptr(talk), _code(talk) if talk is not None else 0, gate_ptr, gate_ld, out.data_ptr(), n, r,
                 num_heads, num_kv_heads, head_dim, kv_pages.shape[3], int(chunk or 0), float(scale),
-                float(slope_exponent or 0.0), self._stream()), "attention_talk")
+                float(slope_exponent or 0.0), splits, _ptr(parts), self._stream()), "attention_talk")
         _check(self._mix_lib().ifb_attention_talk(
             q.data_ptr(), _code(q), kv_pages.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), cu_q.data_ptr(),
             seq_lens.data_ptr(), _ptr(talk), _code(talk) if talk is not None else 0, gate_ptr, gate_ld, out.data_ptr(), n, r,
             num_heads, num_kv_heads, head_dim, kv_pages.shape[3], int(chunk or 0), float(scale), float(slope_exponent or 0.0),
             self._stream()), "attention_talk")
+
+    def _talk_splits(self, n, r, num_heads, head_dim, chunk, max_q_len, max_seq_len):
+        """CTAs that share the keys of one query tile of the tensor-core talking attention: 1 unless the step's tiles
+        alone leave most SMs idle (few query tokens) and a query may see many keys; then enough to fill the device
+        once, with no fewer than four tiles of 32 keys each.  Up to 4 for a prompt of few tiles (see below)."""
+        if not max_q_len or not max_seq_len:
+            return 1
+        reach = min(chunk, max_seq_len) if chunk else max_seq_len
+        tiles = (-(-n // 16) + r) * -(-num_heads // 16)
+        if max_q_len > 64:
+            # a prompt: a tile late in its chunk has many times the keys of an early one, and with less than two CTAs
+            # per SM the longest tile is the kernel's time; shares of at most a quarter of the keys even that out
+            return max(1, min(4, reach // 128)) if tiles < 2 * self.sm_count else 1
+        return max(1, min(self.sm_count // max(1, tiles), reach // 128, 32))
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):

@@ -53,7 +53,8 @@ class TalkingAttention:
         out = ctx.buffer("ta_out", (n, self.qw), self.rt.act_dtype)
         k.attention_talk(q, s.num_heads, s.num_kv_heads, s.head_dim, kv.pages, kv.block_tables, ctx.cu_q, ctx.seq_lens, out,
                          s.scale, chunk=s.chunk or 0, slope_exponent=s.slope_exponent or 0.0, talk=self.talk,
-                         gate=proj if self.gate_col >= 0 else None, gate_col=max(self.gate_col, 0), max_q_len=ctx.max_q_len)
+                         gate=proj if self.gate_col >= 0 else None, gate_col=max(self.gate_col, 0), max_q_len=ctx.max_q_len,
+                         max_seq_len=ctx.max_seq_len)
         delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
         k.linear(out, self.w_o, delta)
         return delta

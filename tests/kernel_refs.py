@@ -260,7 +260,7 @@ class ReferenceKernels:
             state[int(state_slots[r])] = S.to(state.dtype)
 
     def attention_talk(self, q, num_heads, num_kv_heads, head_dim, kv_pages, block_tables, cu_q, seq_lens, out, scale,
-                       chunk=0, slope_exponent=0.0, talk=None, gate=None, gate_col=0, max_q_len=0):
+                       chunk=0, slope_exponent=0.0, talk=None, gate=None, gate_col=0, max_q_len=0, max_seq_len=0):
         """Per request, the query at position p sees keys (p // chunk) * chunk .. p (chunk 0: 0 .. p) from the pages:
         a[j] = scale * q_j . k - slope_j * (p - s); b = talk @ a over the heads; softmax over the keys; o = P V;
         out = o * sigmoid(gate)."""

@@ -189,7 +189,8 @@ def _attention_case(K, H, G, d, ps, chunk, dtype, lens_and_new, seed, talk=True,
     got = torch.zeros(n, H * d, device="cuda", dtype=dtype)
     K.attention_talk(pq.cuda(), H, G, d, pp.cuda(), bt_dev.cuda(), cu_t.cuda(), seq.cuda(), got, 0.3, chunk=chunk,
                      slope_exponent=slope, talk=tk.cuda() if talk else None, gate=gt.cuda() if gate else None,
-                     gate_col=7 if gate else 0, max_q_len=max(new for _, new in lens_and_new))
+                     gate_col=7 if gate else 0, max_q_len=max(new for _, new in lens_and_new),
+                     max_seq_len=max(L for L, _ in lens_and_new))
     return got, want
 
 
@@ -205,6 +206,17 @@ def test_talking_attention_kernel(K, H, G, d, ps, chunk, dtype):
     got, want = _attention_case(K, H, G, d, ps, chunk, dtype, cases, seed=H * d + chunk)
     close(got, want, 2e-5 if dtype == torch.float32 else 0.06, "attention")
     assert (K.talk_mma_calls > before) == (dtype == torch.bfloat16 and d in (16, 32, 64, 128))      # which kernel ran
+
+
+@pytest.mark.parametrize("chunk", [512, 0, 300])
+def test_talking_attention_with_the_keys_split_over_ctas(K, chunk):
+    """Decoded tokens over long contexts: the keys of a query are shared out to several CTAs and merged; a request
+    shorter than one share, one at a chunk's first position and a padding row are among them."""
+    cases = [(700, 1), (33, 1), (1500, 1), (0, 1), (512, 1), (513, 1), (1, 1), (1024, 2)]
+    before = K.talk_split_calls
+    got, want = _attention_case(K, 8, 2, 64, 16, chunk, torch.bfloat16, cases, seed=chunk + 1)
+    assert K.talk_split_calls == before + 1
+    close(got, want, 0.06, "split keys")
 
 
 def test_talking_attention_variants(K):
@@ -223,7 +235,7 @@ def test_a_far_key_and_the_keys_at_a_chunks_edge(K, dtype):
             L = 1100 if key_pos > 1000 else 790
             got, want = _attention_case(K, 4, 4, 16, 16, 400, dtype, [(L, new)], seed=11, talk=False, gate=False, slope=0.0,
                                         plant=(key_pos, 400.0))
-            close(got, want, 2e-5 if dtype == torch.float32 else 0.08, f"planted key at {key_pos}, portion of {new}")
+            close(got, want, 1e-4 if dtype == torch.float32 else 0.08, f"planted key at {key_pos}, portion of {new}")      # values of size 9
             assert (float(got[-1].float().abs().min()) > 8.9) == seen, (key_pos, new)
 
 

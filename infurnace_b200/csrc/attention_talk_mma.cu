@@ -118,6 +118,7 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
     }
 
   const int chunk = a.chunk;
+  const int ps_shift = (a.page_size & (a.page_size - 1)) == 0 ? __ffs(a.page_size) - 1 : -1;
   const int first = chunk > 0 ? (p0 / chunk) * chunk : 0;           // the first key any row of the tile sees
   const int* bt = a.block_tables + (size_t)r * a.bt_stride;
   const size_t head_stride = (size_t)a.page_size * D, page_stride = 2 * (size_t)G * head_stride;
@@ -140,8 +141,10 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
       bf16* dst = (is_v ? Vs + ((size_t)(gg - G) * TM_KEYS + j) * LD : Ks + ((size_t)g * TM_KEYS + j) * LD) + c * 8;
       const int key = k0 + j;
       if (key <= p_last) {
-        const bf16* src = a.pages + (size_t)bt[key / a.page_size] * page_stride + ((size_t)(is_v ? G : 0) + g) * head_stride +
-                          (size_t)(key % a.page_size) * D + c * 8;
+        const int pi = ps_shift >= 0 ? key >> ps_shift : key / a.page_size;           // pages are nearly always 2^k tokens
+        const int po = ps_shift >= 0 ? key & (a.page_size - 1) : key % a.page_size;
+        const bf16* src = a.pages + (size_t)bt[pi] * page_stride + ((size_t)(is_v ? G : 0) + g) * head_stride +
+                          (size_t)po * D + c * 8;
         tm_cp16(dst, src);
       } else {
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);

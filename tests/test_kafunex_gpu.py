@@ -341,3 +341,27 @@ def test_greedy_generation_through_the_engine_and_its_graphs(models):
         assert (eng.runner.graph_replays > 0) == graphs
         eng.runner.cache.check()
         assert eng.runner.cache.num_free_slots == 4
+
+
+def test_command_line_and_random_weights(models, tmp_path):
+    """The command line on a model folder of this design (greedy: the plain implementation's tokens), and random weights
+    drawn from a configuration file that names its architecture with the single key."""
+    import json
+    import os
+    import subprocess
+    import sys
+    d, cfg, w, _, _ = models["K1"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bin", "infurnace-b200"), "--model", d, "--prompt-ids", "5,6,7,8",
+                          "--max-tokens", "6", "--json", "--dtype", "float32", "--page-size", "16", "--max-context", "64"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    report = json.loads(out.stdout)
+    assert report["generated_token_ids"] == P.greedy(cfg, w, [5, 6, 7, 8], 6) and report["model"]["architecture"] == "Kafunex"
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(TK.TINY["K2"]["config"]))
+    out = subprocess.run([sys.executable, "-m", "infurnace_b200", "--random-weights", "3", "--config", str(cfg_path),
+                          "--prompt", "hello", "--char-tokenizer", "--max-tokens", "5", "--page-size", "8", "--max-context", "64",
+                          "--json"], capture_output=True, text=True, timeout=600, cwd=root)
+    assert out.returncode == 0, out.stderr
+    assert len(json.loads(out.stdout)["generated_token_ids"]) == 5

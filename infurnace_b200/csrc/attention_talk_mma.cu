@@ -3,16 +3,18 @@
 //
 // A CTA owns a tile of 16 query tokens of one request and a group of NW output heads, one per warp.  Keys of the
 // tile's chunk are taken 32 at a time:
-//   1. K of every key/value head and V of the group's key/value heads come into shared memory (16-byte async copies);
-//   2. the warps form the raw scores of ALL query heads, S_h = Q_h K_g^T (the mixing needs every head's score of a
-//      (query, key) pair), scale them, subtract the distance bias and leave them in shared memory in float32;
-//   3. the block mixes: for its pair (query, key) a thread forms b[o] = sum_h talk[o][h] * a[h] for the group's
-//      heads o, in float32 on the ordinary pipes (the scores are never rounded);
+//   1. K and V of the group's key/value heads come into shared memory (16-byte async copies);
+//   2. warp w forms the raw scores of its head, S = Q K_g^T, scales them, subtracts the distance bias and leaves
+//      them in shared memory in float32;
+//   3. the block mixes: a thread forms b[o] = sum_h talk[o][h] * a[h] for four heads o of the group and four
+//      neighbouring keys of one query, in float32 on the ordinary pipes (the scores are never rounded);
 //   4. warp w carries head o = group * NW + w: running maximum and sum per row, P rounded to bfloat16 as the A
 //      operand of O += P V, V read transposed from shared memory.
-// With more query heads than NW the groups are CTAs of their own, each of which forms the raw scores again (tensor
-// work that is cheap beside step 3, whose cost does not depend on the split).  The output is multiplied by
-// sigmoid(gate) and stored as bfloat16.  Head sizes 16, 32, 64, 128.
+// The mixing needs every head's score of a (query, key) pair.  With more query heads than NW (16) the groups of one
+// query tile are the CTAs of a thread-block cluster: each scores its own heads, and step 3 reads the other groups'
+// scores out of their shared memory (mapa + ld.shared::cluster) between two cluster barriers, so that no score is
+// formed twice and a CTA holds the queries, keys and values of its own heads only.  The output is multiplied by
+// sigmoid(gate) and stored as bfloat16.  Head sizes 16, 32, 64, 128; up to 8 groups (128 heads).
 // A step of few query tokens (decoding) has few tiles; its keys are then split over several CTAs per tile (each takes
 // every splits-th tile of 32 keys; the mixing is per (query, key) pair, so any split of the keys is exact), and a
 // second kernel merges the parts in a fixed order.
@@ -65,9 +67,24 @@ __device__ __forceinline__ uint32_t tm_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Shared memory, in this order: Q [H][16][D + 8] bf16, K [G][32][D + 8] bf16, V [GV][32][D + 8] bf16 (GV: key/value
-// heads of the group), S [H][16][32] float, M [NW][16][32] float, talk^T [H][NW] float.
-template <int D, int NW>
+// All threads of all CTAs of the cluster: arrive (release) and wait (acquire).  Every CTA of a cluster takes the same
+// number of trips through the key loop (they share the query tile), and none leaves before the last barrier.
+__device__ __forceinline__ void tm_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// Four floats at this CTA's shared address `addr`, read from the CTA of rank `rank` in the cluster.
+__device__ __forceinline__ float4 tm_ld_cluster_f4(uint32_t addr, int rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(addr), "r"(rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
+}
+
+// Shared memory, in this order: Q [NW][16][D + 8] bf16, K and V [GV][32][D + 8] bf16 each (GV: key/value heads of the
+// group), S [NW][16][32] float, M [NW][16][32] float, talk^T [H][NW] float.  CL: the groups form a cluster.
+template <int D, int NW, bool CL>
 __global__ void __launch_bounds__(NW * 32, 1)
 attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
   extern __shared__ __align__(16) unsigned char tm_raw[];
@@ -98,17 +115,17 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
   const int g_lo = o0 / rep, g_hi = (o0 + heads_here - 1) / rep, GV = g_hi - g_lo + 1;
 
   bf16* Qs = reinterpret_cast<bf16*>(tm_raw);
-  bf16* Ks = Qs + (size_t)H * TM_ROWS * LD;
-  bf16* Vs = Ks + (size_t)G * TM_KEYS * LD;
+  bf16* Ks = Qs + (size_t)NW * TM_ROWS * LD;
+  bf16* Vs = Ks + (size_t)gv_max * TM_KEYS * LD;
   float* Ss = reinterpret_cast<float*>(Vs + (size_t)gv_max * TM_KEYS * LD);
-  float* Ms = Ss + (size_t)H * TM_ROWS * TM_KEYS;
+  float* Ms = Ss + (size_t)NW * TM_ROWS * TM_KEYS;
   float* Tt = Ms + (size_t)NW * TM_ROWS * TM_KEYS;                  // [H][NW]: talk[o0 + o][h] at Tt[h * NW + o]
 
   constexpr int CH = D / 8;                                         // 16-byte pieces of a head row
-  for (int idx = tid; idx < H * TM_ROWS * CH; idx += NW * 32) {
+  for (int idx = tid; idx < heads_here * TM_ROWS * CH; idx += NW * 32) {
     const int c = idx % CH, i = (idx / CH) % TM_ROWS, h = idx / (CH * TM_ROWS);
     bf16* dst = Qs + ((size_t)h * TM_ROWS + i) * LD + c * 8;
-    if (i < rows) tm_cp16(dst, a.q + (size_t)(q0 + i) * H * D + (size_t)h * D + c * 8);
+    if (i < rows) tm_cp16(dst, a.q + (size_t)(q0 + i) * H * D + (size_t)(o0 + h) * D + c * 8);
     else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
   }
   if (a.talk)
@@ -134,11 +151,11 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
 
   for (int k0 = first + (int)blockIdx.z * TM_KEYS; k0 <= p_last; k0 += TM_KEYS * a.splits) {
     // ---- 1. keys and values of this tile
-    for (int idx = tid; idx < (G + GV) * TM_KEYS * CH; idx += NW * 32) {
+    for (int idx = tid; idx < 2 * GV * TM_KEYS * CH; idx += NW * 32) {
       const int c = idx % CH, j = (idx / CH) % TM_KEYS, gg = idx / (CH * TM_KEYS);
-      const bool is_v = gg >= G;
-      const int g = is_v ? g_lo + (gg - G) : gg;
-      bf16* dst = (is_v ? Vs + ((size_t)(gg - G) * TM_KEYS + j) * LD : Ks + ((size_t)g * TM_KEYS + j) * LD) + c * 8;
+      const bool is_v = gg >= GV;
+      const int g = g_lo + (is_v ? gg - GV : gg);
+      bf16* dst = (is_v ? Vs : Ks) + ((size_t)(g - g_lo) * TM_KEYS + j) * LD + c * 8;
       const int key = k0 + j;
       if (key <= p_last) {
         const int pi = ps_shift >= 0 ? key >> ps_shift : key / a.page_size;           // pages are nearly always 2^k tokens
@@ -152,13 +169,14 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
     }
     tm_cp_wait();
     __syncthreads();
-    // ---- 2. raw scores of every query head
-    for (int h = warp; h < H; h += NW) {
+    // ---- 2. raw scores of this warp's head
+    if (warp < heads_here) {
+      const int h = o0 + warp;
       float acc[4][4];
 #pragma unroll
       for (int n = 0; n < 4; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
-      const bf16* qh = Qs + (size_t)h * TM_ROWS * LD;
-      const bf16* kg = Ks + (size_t)(h / rep) * TM_KEYS * LD;
+      const bf16* qh = Qs + (size_t)warp * TM_ROWS * LD;
+      const bf16* kg = Ks + (size_t)(h / rep - g_lo) * TM_KEYS * LD;
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         uint32_t af[4];
@@ -172,7 +190,7 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
         }
       }
       const float slope = a.slope_exp > 0.f ? exp2f(-a.slope_exp * (float)(h + 1) / (float)H) : 0.f;
-      float* sh = Ss + (size_t)h * TM_ROWS * TM_KEYS;
+      float* sh = Ss + (size_t)warp * TM_ROWS * TM_KEYS;
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
         const int col = n * 8 + cl, key = k0 + col;
@@ -182,9 +200,9 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
         *reinterpret_cast<float2*>(sh + (rl + 8) * TM_KEYS + col) = v1;
       }
     }
-    __syncthreads();
+    if (CL) tm_cluster_sync(); else __syncthreads();      // every group's scores are in its shared memory
     // ---- 3. the heads' scores of each (query, key) pair mixed, for the group's heads
-    const float* Sc = Ss + (size_t)o0 * TM_ROWS * TM_KEYS;          // without mixing: the group's own scores
+    const float* Sc = Ss;                                           // without mixing: the group's own scores
     if (a.talk) {
       // a thread takes four neighbouring keys of one query and four heads of the group: per source head one 16-byte
       // load of scores, one of weights (the same for the whole warp) and sixteen multiply-adds
@@ -192,8 +210,10 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
       float b[4][4];
 #pragma unroll
       for (int o = 0; o < 4; ++o) { b[o][0] = b[o][1] = b[o][2] = b[o][3] = 0.f; }
+      const uint32_t s_at = tm_smem(Ss) + (uint32_t)(pq * 16);
       for (int h = 0; h < H; ++h) {
-        const float4 s4 = *reinterpret_cast<const float4*>(Ss + (size_t)h * TM_ROWS * TM_KEYS + pq * 4);
+        const float4 s4 = CL ? tm_ld_cluster_f4(s_at + (uint32_t)((h % NW) * TM_ROWS * TM_KEYS * 4), h / NW)
+                             : *reinterpret_cast<const float4*>(Ss + (size_t)h * TM_ROWS * TM_KEYS + pq * 4);
         const float4 t4 = *reinterpret_cast<const float4*>(Tt + h * NW + oq * 4);
         b[0][0] = fmaf(t4.x, s4.x, b[0][0]); b[0][1] = fmaf(t4.x, s4.y, b[0][1]); b[0][2] = fmaf(t4.x, s4.z, b[0][2]); b[0][3] = fmaf(t4.x, s4.w, b[0][3]);
         b[1][0] = fmaf(t4.y, s4.x, b[1][0]); b[1][1] = fmaf(t4.y, s4.y, b[1][1]); b[1][2] = fmaf(t4.y, s4.z, b[1][2]); b[1][3] = fmaf(t4.y, s4.w, b[1][3]);
@@ -203,9 +223,10 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
 #pragma unroll
       for (int o = 0; o < 4; ++o)
         *reinterpret_cast<float4*>(Ms + (size_t)(oq * 4 + o) * TM_ROWS * TM_KEYS + pq * 4) = make_float4(b[o][0], b[o][1], b[o][2], b[o][3]);
-      __syncthreads();
       Sc = Ms;
     }
+    // the mixed scores are in place; and nobody writes its scores of the next tile while a peer still reads these
+    if (CL) tm_cluster_sync(); else __syncthreads();
     // ---- 4. softmax step and O += P V for this warp's head
     if (warp < heads_here) {
       const float* sw = Sc + (size_t)warp * TM_ROWS * TM_KEYS;
@@ -340,8 +361,8 @@ attention_talk_merge_kernel(TalkMmaArgs a) {
 }
 
 static size_t tm_smem_bytes(int H, int G, int D, int NW, int gv_max) {
-  return ((size_t)H * TM_ROWS + (size_t)(G + gv_max) * TM_KEYS) * (D + 8) * sizeof(bf16) +
-         ((size_t)(H + NW) * TM_ROWS * TM_KEYS + (size_t)H * NW) * sizeof(float);
+  return ((size_t)NW * TM_ROWS + (size_t)2 * gv_max * TM_KEYS) * (D + 8) * sizeof(bf16) +
+         ((size_t)2 * NW * TM_ROWS * TM_KEYS + (size_t)H * NW) * sizeof(float);
 }
 static int tm_warps(int H) { return H <= 4 ? 4 : H <= 8 ? 8 : 16; }
 static int tm_gv_max(int H, int G, int NW) {        // key/value heads that a group of NW query heads can touch
@@ -359,6 +380,7 @@ static int tm_gv_max(int H, int G, int NW) {        // key/value heads that a gr
 IFB_EXPORT int ifb_attention_talk_mma_fits(int H, int G, int D) {
   if (H < 1 || G < 1 || H % G || (D != 16 && D != 32 && D != 64 && D != 128)) return 0;
   const int NW = tm_warps(H);
+  if ((H + NW - 1) / NW > 8) return 0;                      // the groups of a tile are one cluster
   return tm_smem_bytes(H, G, D, NW, tm_gv_max(H, G, NW)) <= 220 * 1024 ? 1 : 0;
 }
 
@@ -366,9 +388,32 @@ template <int D, int NW>
 static int tm_launch(const TalkMmaArgs& a, cudaStream_t s) {
   const int gv_max = tm_gv_max(a.H, a.G, NW);
   const size_t smem = tm_smem_bytes(a.H, a.G, D, NW, gv_max);
-  IFB_ALLOW_SMEM((attention_talk_mma_kernel<D, NW>), smem);
-  dim3 grid((a.n_tokens + TM_ROWS - 1) / TM_ROWS + a.n_req, (a.H + NW - 1) / NW, a.splits);
-  const int st = ifb_launch(attention_talk_mma_kernel<D, NW>, grid, dim3(NW * 32), smem, s, a, gv_max);
+  const int groups = (a.H + NW - 1) / NW;
+  dim3 grid((a.n_tokens + TM_ROWS - 1) / TM_ROWS + a.n_req, groups, a.splits);
+  int st;
+  if (groups == 1) {
+    IFB_ALLOW_SMEM((attention_talk_mma_kernel<D, NW, false>), smem);
+    st = ifb_launch(attention_talk_mma_kernel<D, NW, false>, grid, dim3(NW * 32), smem, s, a, gv_max);
+  } else {                                                  // the groups of a query tile: one cluster along y
+    IFB_ALLOW_SMEM((attention_talk_mma_kernel<D, NW, true>), smem);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = groups;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ifb_pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_talk_mma_kernel<D, NW, true>, a, gv_max);
+    if (e != cudaSuccess) { cudaGetLastError(); return -(int)e; }
+    st = IFB_OK;
+  }
   if (st != IFB_OK || a.splits == 1) return st;
   const long long items = (long long)a.n_tokens * a.H;
   return ifb_launch(attention_talk_merge_kernel<D>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, a);

@@ -131,7 +131,7 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, "object"]], metada
             if callable(t):
                 t = t()
             t = t.detach().contiguous().cpu()
-            raw = t.view(torch.uint8) if t.numel() else t
+            raw = t.reshape(-1).view(torch.uint8) if t.numel() else t      # reshape: a tensor of shape () has no axis to view
             data = raw.numpy().tobytes() if t.numel() else b""
             if len(data) != nbytes:
                 raise WeightError(f"tensor {name} produced {len(data)} bytes, expected {nbytes}")

@@ -196,7 +196,8 @@ def _attention_case(K, H, G, d, ps, chunk, dtype, lens_and_new, seed, talk=True,
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,ps,chunk", [(4, 2, 16, 16, 24), (6, 6, 8, 8, 0), (3, 1, 24, 8, 32), (8, 2, 64, 16, 100),
-                                            (5, 5, 40, 4, 9), (2, 1, 128, 32, 300), (16, 4, 32, 16, 64)])
+                                            (5, 5, 40, 4, 9), (2, 1, 128, 32, 300), (16, 4, 32, 16, 64),
+                                            (32, 8, 64, 16, 128), (24, 6, 32, 8, 50), (40, 8, 16, 16, 0)])
 def test_talking_attention_kernel(K, H, G, d, ps, chunk, dtype):
     """Whole prompts, portions that begin and end inside a chunk and inside a page, single tokens just before, on
     and after a chunk's edge, and a padding row."""
@@ -204,7 +205,7 @@ def test_talking_attention_kernel(K, H, G, d, ps, chunk, dtype):
     cases = [(70, 70), (c + 1, 1), (c, 1), (2 * c - 1, 1), (2 * c + 5, c + 3), (1, 1), (3 * c + 2, 2), (0, 1), (210, 1)]
     before = K.talk_mma_calls
     got, want = _attention_case(K, H, G, d, ps, chunk, dtype, cases, seed=H * d + chunk)
-    close(got, want, 2e-5 if dtype == torch.float32 else 0.06, "attention")
+    close(got, want, 5e-5 if dtype == torch.float32 else 0.06, "attention")      # outputs of size 3; 32 heads mixed in float32
     assert (K.talk_mma_calls > before) == (dtype == torch.bfloat16 and d in (16, 32, 64, 128))      # which kernel ran
 
 
@@ -213,10 +214,11 @@ def test_talking_attention_with_the_keys_split_over_ctas(K, chunk):
     """Decoded tokens over long contexts: the keys of a query are shared out to several CTAs and merged; a request
     shorter than one share, one at a chunk's first position and a padding row are among them."""
     cases = [(700, 1), (33, 1), (1500, 1), (0, 1), (512, 1), (513, 1), (1, 1), (1024, 2)]
-    before = K.talk_split_calls
-    got, want = _attention_case(K, 8, 2, 64, 16, chunk, torch.bfloat16, cases, seed=chunk + 1)
-    assert K.talk_split_calls == before + 1
-    close(got, want, 0.06, "split keys")
+    for H, G, d in ((8, 2, 64), (32, 4, 32)):               # one group of heads; two groups (a cluster) per tile
+        before = K.talk_split_calls
+        got, want = _attention_case(K, H, G, d, 16, chunk, torch.bfloat16, cases, seed=chunk + H)
+        assert K.talk_split_calls == before + 1
+        close(got, want, 0.06, f"split keys, {H} heads")
 
 
 def test_talking_attention_variants(K):

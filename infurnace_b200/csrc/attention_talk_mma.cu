@@ -211,14 +211,24 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
 #pragma unroll
       for (int o = 0; o < 4; ++o) { b[o][0] = b[o][1] = b[o][2] = b[o][3] = 0.f; }
       const uint32_t s_at = tm_smem(Ss) + (uint32_t)(pq * 16);
-      for (int h = 0; h < H; ++h) {
-        const float4 s4 = CL ? tm_ld_cluster_f4(s_at + (uint32_t)((h % NW) * TM_ROWS * TM_KEYS * 4), h / NW)
-                             : *reinterpret_cast<const float4*>(Ss + (size_t)h * TM_ROWS * TM_KEYS + pq * 4);
-        const float4 t4 = *reinterpret_cast<const float4*>(Tt + h * NW + oq * 4);
-        b[0][0] = fmaf(t4.x, s4.x, b[0][0]); b[0][1] = fmaf(t4.x, s4.y, b[0][1]); b[0][2] = fmaf(t4.x, s4.z, b[0][2]); b[0][3] = fmaf(t4.x, s4.w, b[0][3]);
-        b[1][0] = fmaf(t4.y, s4.x, b[1][0]); b[1][1] = fmaf(t4.y, s4.y, b[1][1]); b[1][2] = fmaf(t4.y, s4.z, b[1][2]); b[1][3] = fmaf(t4.y, s4.w, b[1][3]);
-        b[2][0] = fmaf(t4.z, s4.x, b[2][0]); b[2][1] = fmaf(t4.z, s4.y, b[2][1]); b[2][2] = fmaf(t4.z, s4.z, b[2][2]); b[2][3] = fmaf(t4.z, s4.w, b[2][3]);
-        b[3][0] = fmaf(t4.w, s4.x, b[3][0]); b[3][1] = fmaf(t4.w, s4.y, b[3][1]); b[3][2] = fmaf(t4.w, s4.z, b[3][2]); b[3][3] = fmaf(t4.w, s4.w, b[3][3]);
+      // four source heads at a time: their scores (from a peer's shared memory, in a cluster) are asked for together
+      for (int h0 = 0; h0 < H; h0 += 4) {
+        float4 sv[4], tv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int h = min(h0 + u, H - 1);
+          sv[u] = CL ? tm_ld_cluster_f4(s_at + (uint32_t)((h % NW) * TM_ROWS * TM_KEYS * 4), h / NW)
+                     : *reinterpret_cast<const float4*>(Ss + (size_t)h * TM_ROWS * TM_KEYS + pq * 4);
+          tv[u] = h0 + u < H ? *reinterpret_cast<const float4*>(Tt + h * NW + oq * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float4 s4 = sv[u], t4 = tv[u];
+          b[0][0] = fmaf(t4.x, s4.x, b[0][0]); b[0][1] = fmaf(t4.x, s4.y, b[0][1]); b[0][2] = fmaf(t4.x, s4.z, b[0][2]); b[0][3] = fmaf(t4.x, s4.w, b[0][3]);
+          b[1][0] = fmaf(t4.y, s4.x, b[1][0]); b[1][1] = fmaf(t4.y, s4.y, b[1][1]); b[1][2] = fmaf(t4.y, s4.z, b[1][2]); b[1][3] = fmaf(t4.y, s4.w, b[1][3]);
+          b[2][0] = fmaf(t4.z, s4.x, b[2][0]); b[2][1] = fmaf(t4.z, s4.y, b[2][1]); b[2][2] = fmaf(t4.z, s4.z, b[2][2]); b[2][3] = fmaf(t4.z, s4.w, b[2][3]);
+          b[3][0] = fmaf(t4.w, s4.x, b[3][0]); b[3][1] = fmaf(t4.w, s4.y, b[3][1]); b[3][2] = fmaf(t4.w, s4.z, b[3][2]); b[3][3] = fmaf(t4.w, s4.w, b[3][3]);
+        }
       }
 #pragma unroll
       for (int o = 0; o < 4; ++o)

@@ -229,14 +229,69 @@ gated_scan_carry_kernel(GatedScanArgs a) {
   const size_t hi = e / a.vdim;                    // (head, row): the gate's index
   float* slot = a.state + (size_t)a.state_slots[r] * per + e;
   float S = *slot;
-#pragma unroll 4
-  for (int b = 0; b < blocks; ++b) {
-    float* zp = a.z + (size_t)(first + b) * per + e;
-    const float z = *zp, g = a.decay[(size_t)(first + b) * a.heads * a.dim + hi];
-    *zp = S;
-    S = fmaf(g, S, z);
+  // eight blocks at a time: their loads are all asked for before the chain of multiply-adds that needs them
+  for (int b0 = 0; b0 < blocks; b0 += 8) {
+    float z[8], g[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool in = b0 + j < blocks;
+      z[j] = in ? __ldcg(a.z + (size_t)(first + b0 + j) * per + e) : 0.f;
+      g[j] = in ? __ldg(a.decay + (size_t)(first + b0 + j) * a.heads * a.dim + hi) : 1.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (b0 + j < blocks) a.z[(size_t)(first + b0 + j) * per + e] = S;
+      S = fmaf(g[j], S, z[j]);
+    }
   }
   *slot = S;
+}
+
+// Heads with more than 128 rows: the state stays in device memory.  A block per (request, head), its threads over the
+// columns; per token the activated q and f of the head go through shared memory, every thread updates its columns row
+// by row, and the block normalises the head's output.  Slow (the state crosses the memory bus for every token) and
+// exact; no model met so far has such heads.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_scan_wide_kernel(GatedScanArgs a) {
+  extern __shared__ float sm[];
+  __shared__ float scratch[33];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int r = blockIdx.y, h = blockIdx.x, dim = a.dim, vdim = a.vdim;
+  if (a.seq_lens[r] <= 0) return;
+  float* qs = sm;              // [dim]
+  float* fs = sm + dim;        // [dim]
+  float* os = fs + dim;        // [vdim]
+  float* S = a.state + ((size_t)a.state_slots[r] * a.heads + h) * dim * vdim;
+  for (int t = a.cu_q[r]; t < a.cu_q[r + 1]; ++t) {
+    const float* row = a.proj + (size_t)t * a.ld;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+      const float qr = row[a.q_col + h * dim + i];
+      qs[i] = qr / (1.f + expf(-qr));
+      const float lo = load_as_f32(a.lower, a.w_dtype, h * dim + i);
+      const float z = row[a.f_col + h * dim + i] + load_as_f32(a.bias, a.w_dtype, h * dim + i);
+      fs[i] = lo + (1.f - lo) * (1.f / (1.f + expf(-z)));
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+      const float v = row[a.v_col + h * vdim + c];
+      float o = 0.f;
+      for (int i = 0; i < dim; ++i) {
+        const float sv = fmaf(fs[i], S[(size_t)i * vdim + c], (1.f - fs[i]) * v);
+        S[(size_t)i * vdim + c] = sv;
+        o = fmaf(sv, qs[i], o);
+      }
+      os[c] = o;
+      ss += o * o;
+    }
+    ss = block_sum(ss, scratch);
+    const float rn = 1.f / sqrtf(ss / (float)vdim + a.eps);
+    T* dst = (T*)a.out + ((size_t)t * a.heads + h) * vdim;
+    for (int c = threadIdx.x; c < vdim; c += blockDim.x) dst[c] = from_f32<T>(os[c] * rn * load_as_f32(a.norm_w, a.w_dtype, c));
+    __syncthreads();
+  }
 }
 
 // out[t, h, :] = raw[t, h, :] / sqrt(mean(raw[t, h, :]^2) + eps) * w, a warp per (token, head).
@@ -263,6 +318,12 @@ static int gs_block_threads(int dim, int vdim) {
 
 template <typename T>
 static int gs_launch(GatedScanArgs a, int requests, int tokens, cudaStream_t s) {
+  if (a.dim > 128) {
+    const size_t wide = (size_t)(2 * a.dim + a.vdim) * sizeof(float);
+    if (wide > 200 * 1024) return IFB_ERR_SIZE;
+    IFB_ALLOW_SMEM(gated_scan_wide_kernel<T>, wide);
+    return ifb_launch(gated_scan_wide_kernel<T>, dim3(a.heads, requests), dim3(256), wide, s, a);
+  }
   const int threads = gs_block_threads(a.dim, a.vdim);
   a.slabs = (a.vdim + threads - 1) / threads;
   if (a.slabs > 1 && !a.raw) return IFB_ERR_ARG;
@@ -287,6 +348,7 @@ static int gs_launch(GatedScanArgs a, int requests, int tokens, cudaStream_t s) 
 
 // Slabs of columns that a head of these sizes is split into; with more than one the caller gives `raw`.
 IFB_EXPORT int ifb_gated_scan_slabs(int dim, int vdim) {
+  if (dim > 128) return 1;
   const int threads = gs_block_threads(dim, vdim);
   return (vdim + threads - 1) / threads;
 }
@@ -299,7 +361,7 @@ IFB_EXPORT long long ifb_gated_scan_scratch_floats(int tokens, int requests, int
 
 template <typename T>
 static int gs_run(GatedScanArgs a, int requests, int tokens, float* scratch, cudaStream_t s) {
-  if (!scratch) return gs_launch<T>(a, requests, tokens, s);
+  if (!scratch || a.dim > 128) return gs_launch<T>(a, requests, tokens, s);
   const long long blocks = (tokens + GS_BLOCK - 1) / GS_BLOCK + requests;
   a.z = scratch;
   a.decay = scratch + blocks * a.heads * a.dim * (long long)a.vdim;
@@ -313,7 +375,7 @@ static int gs_run(GatedScanArgs a, int requests, int tokens, float* scratch, cud
   return gs_launch<T>(a, requests, tokens, s);
 }
 
-// dim up to 128, any vdim.  bias, lower and norm_w share one dtype.  raw: float32 [tokens][heads * vdim] scratch, needed
+// Any dim and vdim (dim over 128: the slow kernel with the state in device memory).  bias, lower and norm_w share one dtype.  raw: float32 [tokens][heads * vdim] scratch, needed
 // when ifb_gated_scan_slabs(dim, vdim) > 1.  scratch: null for the one-launch walk (a request per block row); else
 // ifb_gated_scan_scratch_floats(...) floats for the three-launch form, in which blocks of 64 tokens run side by side.
 IFB_EXPORT int ifb_gated_scan(const float* proj, int ld, int q_col, int f_col, int v_col, const void* bias, const void* lower,
@@ -321,7 +383,7 @@ IFB_EXPORT int ifb_gated_scan(const float* proj, int ld, int q_col, int f_col, i
                               const int* seq_lens, void* out, int out_dtype, float* raw, float* scratch, int requests, int tokens,
                               int heads, int dim, int vdim, cudaStream_t stream) {
   if (requests <= 0 || tokens <= 0) return IFB_OK;
-  if (heads < 1 || dim < 1 || vdim < 1 || dim > 128 || requests > 65535) return IFB_ERR_SIZE;
+  if (heads < 1 || dim < 1 || vdim < 1 || requests > 65535) return IFB_ERR_SIZE;
   if (w_dtype != IFB_F32 && w_dtype != IFB_BF16) return IFB_ERR_DTYPE;
   GatedScanArgs a{proj, ld, q_col, f_col, v_col, bias, lower, norm_w, w_dtype, eps, state, state_slots, cu_q, seq_lens, out,
                   raw, heads, dim, vdim, 1, 0, requests, nullptr, nullptr};

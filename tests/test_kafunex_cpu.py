@@ -180,6 +180,28 @@ def test_a_small_pool_is_enough_when_every_layer_is_chunked(tmp_path):
         del TK.TINY["_small"]
 
 
+@pytest.mark.parametrize("layers", [[TK._rec(2, 4, 8, 16), TK._rec(1, 6, 5, None)],
+                                    [TK._attn(2, 2, 8, 0.3, 9, None), TK._attn(4, 1, 4, 0.5, None, 12)],
+                                    [TK._rec(1, 3, 7, None)]])
+def test_models_of_one_kind_of_mixer(tmp_path, layers):
+    """Only recurrences (no key/value group at all), only attention (no state), a single layer without feed-forward."""
+    TK.TINY["_v"] = dict(config=TK._config(50, 24, 1e-5, layers), page_size=4, store="float32", seed=3)
+    try:
+        d = TK.make_model_dir("_v", str(tmp_path))
+    finally:
+        del TK.TINY["_v"]
+    cfg, w = P.read_model(d)
+    reqs = {f"r{i}": tiny.random_tokens(50, n, i) for i, n in enumerate([20, 1, 33, 7, 2, 15])}
+    steps = tiny.schedule_mixed(reqs, max_tokens=128, seed=1)
+    eng = Engine.from_model_dir(d, EngineOptions(dtype="float32", device="cpu", page_size=4, num_pages=32, max_num_seqs=4,
+                                                 max_num_batched_tokens=128), kernels=ReferenceKernels(torch.float64))
+    out = tiny.collect(steps, tiny.run_inprocess(eng.runner, steps), 50)
+    for rid, toks in reqs.items():
+        assert (out[rid] - P.forward(cfg, w, toks)).abs().max() < TOL
+    prompt = tiny.random_tokens(50, 5, 9)
+    assert eng.generate([prompt], SamplingParams(max_tokens=6)) == [P.greedy(cfg, w, prompt, 6)]
+
+
 def test_greedy_generation_through_the_scheduler(models):
     cfg, w = P.read_model(models["K2"])
     eng = engine(models["K2"], "K2", max_num_batched_tokens=24)          # prompts go in as portions beside decoded tokens

@@ -103,7 +103,8 @@ def _scan_inputs(heads, dim, vdim, n, seed):
     return proj, torch.randn(hd, generator=g), 0.05 + 0.9 * torch.rand(hd, generator=g), 1 + 0.2 * torch.randn(vdim, generator=g)
 
 
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 12), (1, 24, 40), (2, 40, 33), (3, 100, 64), (2, 32, 600), (1, 64, 300)])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 8, 12), (1, 24, 40), (2, 40, 33), (3, 100, 64), (2, 32, 600), (1, 64, 300),
+                                            (2, 160, 48)])
 def test_gated_recurrence_kernel(K, heads, dim, vdim):
     """Unequal requests in one call (one of them padding), states that are not zero, and the same tokens cut into
     a prompt, a portion and single tokens: the state carries everything."""
@@ -118,7 +119,7 @@ def test_gated_recurrence_kernel(K, heads, dim, vdim):
     REF.gated_scan(proj, 0, hd, 2 * hd, bias, lower, nw, 1e-5, want_state, slots, torch.tensor(cu, dtype=torch.int32), seq, want,
                    heads, dim, vdim)
     raw = torch.zeros(n, hv, device="cuda") if K.gated_scan_slabs(dim, vdim) > 1 else None
-    assert (raw is not None) == (vdim > 256)
+    assert (raw is not None) == (vdim > 256 and dim <= 128)
     state = state0.cuda()
     got = torch.zeros(n, hv, device="cuda")
     K.gated_scan(proj.cuda(), 0, hd, 2 * hd, bias.cuda(), lower.cuda(), nw.cuda(), 1e-5, state, slots.cuda(),
@@ -141,7 +142,7 @@ def test_gated_recurrence_kernel(K, heads, dim, vdim):
     state3, got3, before = state0.cuda(), torch.zeros(n, hv, device="cuda"), K.scan_blocked_calls
     K.gated_scan(proj.cuda(), 0, hd, 2 * hd, bias.cuda(), lower.cuda(), nw.cuda(), 1e-5, state3, slots.cuda(),
                  torch.tensor(cu, dtype=torch.int32).cuda(), seq.cuda(), got3, heads, dim, vdim, raw=raw, max_q_len=1000)
-    assert K.scan_blocked_calls == before + 1
+    assert K.scan_blocked_calls == before + 1           # (heads of more than 128 rows run their one kernel all the same)
     close(got3[rows], want[rows], 2e-5, "outputs in blocks"), close(state3, want_state, 2e-5, "states in blocks")
     out_bf = torch.zeros(n, hv, device="cuda", dtype=torch.bfloat16)
     K.gated_scan(proj.cuda(), 0, hd, 2 * hd, bias.cuda(), lower.cuda(), nw.cuda(), 1e-5, state0.cuda(), slots.cuda(),

@@ -276,7 +276,7 @@ class DenseMLPSpec:
 
 @dataclass(frozen=True)
 class GatedRecurrenceSpec:
-    """The HGRN2 mixer: linear attention whose forget gate also sets what is written.
+    """The HGRN2 mixer: a gated linear recurrence in which one gate f both decays the state and, as 1 - f, weighs the new value.
 
     Per head a float32 state S [dim, vdim], zero at the start of a sequence:
     q = silu(Q h), f = lower + (1 - lower) * sigmoid(F h + bias), v = V h;
@@ -316,8 +316,8 @@ class TalkingAttentionSpec:
     """Grouped-query softmax attention whose heads' scores are mixed before the softmax.
 
     q = Q h, k = K h.  ``q_norm`` / ``k_norm``: RMSNorm of the WHOLE projection (one statistic per token
-    over all heads) with a weight of that length.  ``values_are_keys``: the values are k as projected,
-    before its norm, and there is no value projection.  No rotation; the position enters as a bias:
+    over all heads) with a weight of that length.  ``values_are_keys``: the unnormalised k doubles as the
+    value and the model has no v matrix.  No rotation; the position enters as a bias:
     a[j] = scale * q_j . k - slope_j * (distance), slope_j = 2^(-slope_exponent * (j + 1) / heads)
     (``slope_exponent`` None: no bias).  ``talk`` [heads, heads]: b[j] = sum_i talk[j, i] a[i]
     (None: b = a).  ``chunk`` c: position p sees s <= p with s // c == p // c (None: every s <= p).
@@ -365,8 +365,8 @@ class TalkingAttentionSpec:
 
 @dataclass(frozen=True)
 class PostNormBlockSpec:
-    """x += scale1 * norm1(mixer(x)); x += scale2 * norm2(ffn(x)).  The sublayers read x itself; the norm
-    is on the sublayer's result; ``mixer_scale`` / ``ffn_scale`` name per-feature vectors (layer scale).
+    """x += scale1 * norm1(mixer(x)); x += scale2 * norm2(ffn(x)).  No norm stands before a sublayer: what it
+    returns is normalised before it is added; ``mixer_scale`` / ``ffn_scale`` name per-feature vectors (layer scale).
     ``ffn`` None: the block has no feed-forward (and neither its norm nor its scale)."""
     hidden_size: int
     mixer: object

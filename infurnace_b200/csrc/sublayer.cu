@@ -130,7 +130,7 @@ IFB_EXPORT int ifb_cast_rows(const float* x, void* out, long long count, cudaStr
 // The q and k projections of a token, each normalised as ONE vector over all its heads:
 //   q_out[n, :]  = q / sqrt(mean(q^2) + eps) * qw        (q: proj[n, 0 : q_width])
 //   key page     = k / sqrt(mean(k^2) + eps) * kw        (k: proj[n, q_width : q_width + k_width])
-//   value page   = k as projected (values_are_keys), or proj[n, v_col : v_col + k_width]
+//   value page   = k before its norm (values_are_keys), or proj[n, v_col : v_col + k_width]
 // written at slot = page * page_size + offset of pages [pages][2][kv_heads][page_size][head_dim]; a negative slot
 // stores nothing.  A null weight leaves that projection unnormalised.  proj is float32; T is the cache's type.
 // ------------------------------------------------------------------------------------------

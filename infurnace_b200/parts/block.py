@@ -59,7 +59,7 @@ register_part(PreNormBlockSpec, PreNormBlock)
 
 
 class PostNormBlock:
-    """x += ls1 * norm(mixer(x)); x += ls2 * norm(ffn(x)): the sublayers read the stream itself and the norm
+    """x += ls1 * norm(mixer(x)); x += ls2 * norm(ffn(x)): no norm stands before a sublayer, and the norm
     (one number as weight) is applied to their result.  Norm, layer scale and addition are one kernel, which in
     bfloat16 mode also leaves the bfloat16 copy of the stream that the next product reads.  The block hands on
     no pending delta: x is up to date when it returns."""

@@ -39,7 +39,7 @@ def close(got, want, tol, what=""):
 
 
 # ------------------------------------------------------------------------------ kernels alone
-@pytest.mark.parametrize("width,table_dtype", [(33, torch.float32), (320, torch.bfloat16), (64, torch.float32)])
+@pytest.mark.parametrize("width,table_dtype", [(33, torch.float32), (336, torch.bfloat16), (64, torch.float32)])
 def test_embedding_with_position_vector(K, width, table_dtype):
     g = gen(width)
     table = torch.randn(50, width, generator=g).to(table_dtype)
@@ -54,7 +54,7 @@ def test_embedding_with_position_vector(K, width, table_dtype):
     assert torch.equal(half.cpu(), got.cpu().to(torch.bfloat16))
 
 
-@pytest.mark.parametrize("rows,width", [(1, 33), (7, 320), (70, 2048), (3, 2052), (2, 5000)])
+@pytest.mark.parametrize("rows,width", [(1, 33), (7, 336), (70, 2048), (3, 2052), (2, 5000)])
 def test_residual_update_with_norm_and_layer_scale(K, rows, width):
     g = gen(rows * width)
     x, y = torch.randn(rows, width, generator=g), 5 * torch.randn(rows, width, generator=g)
@@ -247,7 +247,7 @@ def test_products_with_a_unary_epilogue(K, epilogue):
     """On each product kernel: plain float32, few rows, tensor cores one tile per CTA, shared k range, many rows."""
     g = gen(7)
     for n, o, k, dtype in [(5, 70, 33, torch.float32), (3, 96, 64, torch.bfloat16), (40, 200, 128, torch.bfloat16),
-                           (100, 384, 320, torch.bfloat16), (48, 128, 2048, torch.bfloat16), (700, 512, 256, torch.bfloat16)]:
+                           (100, 416, 288, torch.bfloat16), (48, 128, 2048, torch.bfloat16), (700, 512, 256, torch.bfloat16)]:
         x, w = torch.randn(n, k, generator=g).to(dtype), (torch.randn(o, k, generator=g) / k ** 0.5).to(dtype)
         for out_dtype in (torch.float32, dtype):
             want = torch.zeros(n, o, dtype=torch.float64)

@@ -37,7 +37,7 @@ TINY = {
                                               _rec(2, 40, 33, 16)]),
                page_size=8, store="bfloat16", seed=6),
     # wider: the tensor-core products see k of 256 and 192; a long chunk
-    "K3": dict(config=_config(320, 256, 1e-5, [_attn(8, 2, 32, 0.18, 100, 192), _rec(4, 64, 64, 192), _rec(2, 32, 128, None),
+    "K3": dict(config=_config(331, 256, 1e-5, [_attn(8, 2, 32, 0.18, 100, 192), _rec(4, 64, 64, 192), _rec(2, 32, 128, None),
                                                 _attn(4, 4, 64, 0.125, 48, 320)]),
                page_size=16, store="bfloat16", seed=7),
 }

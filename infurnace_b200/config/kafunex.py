@@ -95,7 +95,7 @@ class KafunexConfig:
                                            "only 'dense' feed-forwards exist in this design")
                 mlp = KafunexMLP("dense", _int(mlp, "ff", where + "mlp."))
             if kind == ATTENTION:
-                kv = _int(m, "kv_heads", where + "mixer.")
+                kv = heads if m.get("kv_heads") is None else _int(m, "kv_heads", where + "mixer.")      # absent: one per query head
                 if heads % kv:
                     raise ModelConfigError(f"config.json: {where}mixer.heads {heads} is not a multiple of kv_heads {kv}")
                 if vdim != dim:

@@ -20,7 +20,6 @@
 // second kernel merges the parts in a fixed order.
 #include "common.cuh"
 #include <math.h>
-#include <mma.h>
 
 typedef __nv_bfloat16 bf16;
 

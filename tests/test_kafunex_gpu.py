@@ -319,6 +319,31 @@ def test_first_tokens_and_long_decoding(models, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_in_portions_then_decoding(models, dtype):
+    """1,500 tokens: portions of 700, 333, 2 and 400 (the recurrence in blocks, attention tiles with shared-out keys,
+    many chunk edges inside portions), then 65 tokens one by one, beside a second request that comes and goes."""
+    d, cfg, w, _, _ = models["K3"]
+    toks = tiny.random_tokens(cfg["vocab"], 1500, 91)
+    other = tiny.random_tokens(cfg["vocab"], 90, 92)
+    want, want_other = P.forward(cfg, w, toks).float(), P.forward(cfg, w, other).float()
+    steps, at = [], 0
+    for i, n in enumerate([700, 333, 2, 400] + [1] * 65):
+        entries = [{"id": "x", "tokens": toks[at:at + n], "want": list(range(n))}]
+        if i == 1:
+            entries.append({"id": "y", "tokens": other[:60], "want": list(range(60))})
+        if 2 <= i < 32:
+            entries.append({"id": "y", "tokens": [other[58 + i]], "want": [0]})
+        steps.append({"step": i, "entries": entries, "end": ["y"] if i == 31 else []})
+        at += n
+    assert at == 1500
+    out = tiny.collect(steps, tiny.run_inprocess(_runner(d, "K3", dtype, 1664), steps), cfg["vocab"])
+    tol = F32_TOL * 2 if dtype == "float32" else bf16_tol([want])
+    err = (out["x"] - want).abs().max(dim=-1).values
+    assert float(err.max()) <= tol, f"position {int(err.argmax())}: {float(err.max())}"
+    assert float((out["y"] - want_other).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(models, tmp_path, dtype):
     d, cfg, w, reqs, ref = models["K2"]
     steps = tiny.schedule_mixed(reqs, max_live=4, max_tokens=512, seed=5)

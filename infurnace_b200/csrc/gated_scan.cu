@@ -66,7 +66,8 @@ __device__ __forceinline__ bool gs_find_block(const GatedScanArgs& a, int row, i
 
 constexpr int gs_max_threads(int dmax) { return dmax <= 32 ? 512 : dmax <= 64 ? 256 : 128; }
 
-template <typename T, int DMAX>
+// OUT false (launch A only): the walk leaves no outputs, so the sums S^T q are not formed.
+template <typename T, int DMAX, bool OUT>
 __global__ void __launch_bounds__(gs_max_threads(DMAX), 1)
 gated_scan_kernel(GatedScanArgs a) {
   extern __shared__ float sm[];
@@ -176,11 +177,16 @@ gated_scan_kernel(GatedScanArgs a) {
         float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
         for (int i = 0; i < DMAX / 4; ++i) {
-          const float4 fi = f[i], qi = q[i];
-          S[4 * i] = fmaf(fi.x, S[4 * i], (1.f - fi.x) * v);             o0 = fmaf(S[4 * i], qi.x, o0);
-          S[4 * i + 1] = fmaf(fi.y, S[4 * i + 1], (1.f - fi.y) * v);     o1 = fmaf(S[4 * i + 1], qi.y, o1);
-          S[4 * i + 2] = fmaf(fi.z, S[4 * i + 2], (1.f - fi.z) * v);     o2 = fmaf(S[4 * i + 2], qi.z, o2);
-          S[4 * i + 3] = fmaf(fi.w, S[4 * i + 3], (1.f - fi.w) * v);     o3 = fmaf(S[4 * i + 3], qi.w, o3);
+          const float4 fi = f[i];
+          S[4 * i] = fmaf(fi.x, S[4 * i], (1.f - fi.x) * v);
+          S[4 * i + 1] = fmaf(fi.y, S[4 * i + 1], (1.f - fi.y) * v);
+          S[4 * i + 2] = fmaf(fi.z, S[4 * i + 2], (1.f - fi.z) * v);
+          S[4 * i + 3] = fmaf(fi.w, S[4 * i + 3], (1.f - fi.w) * v);
+          if (OUT) {
+            const float4 qi = q[i];
+            o0 = fmaf(S[4 * i], qi.x, o0); o1 = fmaf(S[4 * i + 1], qi.y, o1);
+            o2 = fmaf(S[4 * i + 2], qi.z, o2); o3 = fmaf(S[4 * i + 3], qi.w, o3);
+          }
         }
         os[t * blockDim.x + threadIdx.x] = (o0 + o1) + (o2 + o3);
       }
@@ -335,8 +341,13 @@ static int gs_launch(GatedScanArgs a, int requests, int tokens, cudaStream_t s) 
   if (!done && a.dim <= D) {                                                           \
     const size_t smem = ((size_t)GS_GROUP * (2 * D + 2 * threads) + D) * sizeof(float); \
     done = true;                                                                       \
-    IFB_ALLOW_SMEM((gated_scan_kernel<T, D>), smem);                                   \
-    st = ifb_launch(gated_scan_kernel<T, D>, grid, dim3(threads), smem, s, a);         \
+    if (a.mode == 1) {                                                                 \
+      IFB_ALLOW_SMEM((gated_scan_kernel<T, D, false>), smem);                          \
+      st = ifb_launch(gated_scan_kernel<T, D, false>, grid, dim3(threads), smem, s, a); \
+    } else {                                                                           \
+      IFB_ALLOW_SMEM((gated_scan_kernel<T, D, true>), smem);                           \
+      st = ifb_launch(gated_scan_kernel<T, D, true>, grid, dim3(threads), smem, s, a); \
+    }                                                                                  \
   }
   GS_CASE(16) GS_CASE(32) GS_CASE(64) GS_CASE(128)
 #undef GS_CASE

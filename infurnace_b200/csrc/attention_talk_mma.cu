@@ -3,7 +3,8 @@
 //
 // A CTA owns a tile of 16 query tokens of one request and a group of NW output heads, one per warp.  Keys of the
 // tile's chunk are taken 32 at a time:
-//   1. K and V of the group's key/value heads come into shared memory (16-byte async copies);
+//   1. K and V of the group's key/value heads come into shared memory (16-byte async copies, asked for one tile ahead:
+//      the keys while the tile before is mixed and consumed, the values while this tile's scores are formed and mixed);
 //   2. warp w forms the raw scores of its head, S = Q K_g^T, scales them, subtracts the distance bias and leaves
 //      them in shared memory in float32;
 //   3. the block mixes: a thread forms b[o] = sum_h talk[o][h] * a[h] for four heads o of the group and four
@@ -48,6 +49,8 @@ __device__ __forceinline__ void tm_cp16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(tm_smem(dst)), "l"(src));
 }
 __device__ __forceinline__ void tm_cp_wait() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory"); }
+__device__ __forceinline__ void tm_cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void tm_cp_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 __device__ __forceinline__ void tm_ldsm4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(tm_smem(p)));
@@ -148,13 +151,15 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
   for (int n = 0; n < D / 8; ++n) { O[n][0] = O[n][1] = O[n][2] = O[n][3] = 0.f; }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-  for (int k0 = first + (int)blockIdx.z * TM_KEYS; k0 <= p_last; k0 += TM_KEYS * a.splits) {
-    // ---- 1. keys and values of this tile
-    for (int idx = tid; idx < 2 * GV * TM_KEYS * CH; idx += NW * 32) {
+  // The copies of a tile's keys are asked for while the tile before it is mixed and consumed, those of its values while
+  // its own scores are formed and mixed: K's buffer is free once the scores are out, V's once the tile is consumed.  Every
+  // thread commits the same groups in the same order (K0 with the queries, V0, K1, V1, ...), so "all but the latest
+  // group" is K of the present tile at the top of a trip and V of the present tile before its fourth step.
+  auto load_tile = [&](int k0, bool is_v) {
+    for (int idx = tid; idx < GV * TM_KEYS * CH; idx += NW * 32) {
       const int c = idx % CH, j = (idx / CH) % TM_KEYS, gg = idx / (CH * TM_KEYS);
-      const bool is_v = gg >= GV;
-      const int g = g_lo + (is_v ? gg - GV : gg);
-      bf16* dst = (is_v ? Vs : Ks) + ((size_t)(g - g_lo) * TM_KEYS + j) * LD + c * 8;
+      const int g = g_lo + gg;
+      bf16* dst = (is_v ? Vs : Ks) + ((size_t)gg * TM_KEYS + j) * LD + c * 8;
       const int key = k0 + j;
       if (key <= p_last) {
         const int pi = ps_shift >= 0 ? key >> ps_shift : key / a.page_size;           // pages are nearly always 2^k tokens
@@ -166,7 +171,15 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
     }
-    tm_cp_wait();
+  };
+  const int k_first = first + (int)blockIdx.z * TM_KEYS, k_step = TM_KEYS * a.splits;
+  if (k_first <= p_last) load_tile(k_first, false);
+  tm_cp_commit();
+  if (k_first <= p_last) load_tile(k_first, true);
+  tm_cp_commit();
+  for (int k0 = k_first; k0 <= p_last; k0 += k_step) {
+    // ---- 1. this tile's keys have landed (its values may still be on their way)
+    tm_cp_wait_but_one();
     __syncthreads();
     // ---- 2. raw scores of this warp's head
     if (warp < heads_here) {
@@ -200,6 +213,8 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
       }
     }
     if (CL) tm_cluster_sync(); else __syncthreads();      // every group's scores are in its shared memory
+    if (k0 + k_step <= p_last) load_tile(k0 + k_step, false);      // K's buffer is free: the next tile's keys
+    tm_cp_commit();
     // ---- 3. the heads' scores of each (query, key) pair mixed, for the group's heads
     const float* Sc = Ss;                                           // without mixing: the group's own scores
     if (a.talk) {
@@ -234,6 +249,7 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
         *reinterpret_cast<float4*>(Ms + (size_t)(oq * 4 + o) * TM_ROWS * TM_KEYS + pq * 4) = make_float4(b[o][0], b[o][1], b[o][2], b[o][3]);
       Sc = Ms;
     }
+    tm_cp_wait_but_one();                                 // this tile's values have landed (the next keys may be on their way)
     // the mixed scores are in place; and nobody writes its scores of the next tile while a peer still reads these
     if (CL) tm_cluster_sync(); else __syncthreads();
     // ---- 4. softmax step and O += P V for this warp's head
@@ -286,6 +302,8 @@ attention_talk_mma_kernel(TalkMmaArgs a, int gv_max) {
       }
     }
     __syncthreads();
+    if (k0 + k_step <= p_last) load_tile(k0 + k_step, true);       // V's buffer is free: the next tile's values
+    tm_cp_commit();
   }
   tm_cp_wait();                             // a CTA without a tile of keys has the copies of its queries in flight
   if (warp >= heads_here) return;

@@ -741,6 +741,73 @@ def run_designs(args):
     return 0
 
 
+def time_design_kernels(args):
+    """The talking attention and the gated recurrence alone, on tensors made on the device at the sizes of design_configs:
+    a 2,048-token prompt, four such prompts in one step, and a decode step of 8 requests 2,040 tokens in.  Microseconds
+    by CUDA events over 20 calls after 3; one JSON line.  (Also the small case for a profiler: --design-sizes s.)"""
+    import torch
+    from infurnace_b200.kernels import load_cuda_kernels
+    K = load_cuda_kernels()
+    g = torch.Generator(device="cuda").manual_seed(1)
+
+    def timed(f, reps=20):
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            f()
+        e.record()
+        torch.cuda.synchronize()
+        return round(s.elapsed_time(e) / reps * 1e3, 1)
+
+    def step_arrays(lens_new):
+        news = [n for _, n in lens_new]
+        cu = torch.tensor([0] + [sum(news[:i + 1]) for i in range(len(news))], dtype=torch.int32, device="cuda")
+        return cu, torch.tensor([L for L, _ in lens_new], dtype=torch.int32, device="cuda"), sum(news)
+
+    def attention(H, G, d, chunk, lens_new, ps=16):
+        cu, seq, n = step_arrays(lens_new)
+        R, maxp = len(lens_new), max(-(-L // ps) for L, _ in lens_new)
+        pages = torch.randn(R * maxp + 1, 2, G, ps, d, device="cuda", generator=g).bfloat16()
+        bt = torch.arange(R * maxp, dtype=torch.int32, device="cuda").view(R, maxp).contiguous()
+        q = torch.randn(n, H * d, device="cuda", generator=g).bfloat16()
+        talk = (torch.eye(H, device="cuda") + 0.3 * torch.randn(H, H, device="cuda", generator=g)).bfloat16()
+        gate = torch.randn(n, H * d, device="cuda", generator=g)
+        out = torch.empty_like(q)
+        mq, ms = max(x for _, x in lens_new), max(L for L, _ in lens_new)
+        return timed(lambda: K.attention_talk(q, H, G, d, pages, bt, cu, seq, out, d ** -0.5, chunk=chunk, slope_exponent=8.0,
+                                              talk=talk, gate=gate, max_q_len=mq, max_seq_len=ms))
+
+    def recurrence(heads, dim, vdim, lens_new):
+        cu, seq, n = step_arrays(lens_new)
+        R, hd, hv = len(lens_new), heads * dim, heads * vdim
+        proj = torch.randn(n, 2 * hd + hv, device="cuda", generator=g)
+        state = torch.zeros(R, heads, dim, vdim, device="cuda")
+        out = torch.empty(n, hv, device="cuda", dtype=torch.bfloat16)
+        bias, lower, nw = (torch.rand(k, device="cuda", generator=g).bfloat16() for k in (hd, hd, vdim))
+        slots = torch.arange(R, dtype=torch.int32, device="cuda")
+        mq = max(x for _, x in lens_new)
+        return timed(lambda: K.gated_scan(proj, 0, hd, 2 * hd, bias, lower, nw, 1e-5, state, slots, cu, seq, out, heads, dim, vdim,
+                                          max_q_len=mq))
+
+    prompt, four, decode = [(PREFILL_TOKENS, PREFILL_TOKENS)], [(PREFILL_TOKENS, PREFILL_TOKENS)] * 4, [(2041, 1)] * 8
+    out = {}
+    for size in args.design_sizes.split(","):
+        kaf, _ = design_configs(size)
+        a = next(e["mixer"] for e in kaf["layers"] if e["type"] == "attention")
+        r = next(e["mixer"] for e in kaf["layers"] if e["type"] == "hgrn2")
+        att = (a["heads"], a["kv_heads"], a["dim"], a["mask"]["size"])
+        rec = (r["heads"], r["dim"], r["vdim"])
+        out[size] = {"attention_us": {"prompt": attention(*att, prompt), "four_prompts": attention(*att, four),
+                                      "decode_b8": attention(*att, decode)},
+                     "recurrence_us": {"prompt": recurrence(*rec, prompt), "decode_b8": recurrence(*rec, decode)}}
+    print(json.dumps({"metric": "design_kernels_alone", "unit": "us", "dtype": "bfloat16", "sizes": out,
+                      "tensor_core_attention_calls": K.talk_mma_calls, "blocked_recurrence_calls": K.scan_blocked_calls}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -759,6 +826,8 @@ def main():
     ap.add_argument("--designs", action="store_true",
                     help="instead of the default workload: the Kafunex design beside Qwen3 at equal sizes (prefill and decode)")
     ap.add_argument("--design-sizes", default="s,m", help="with --designs: which of the sizes s, m, l (commas between)")
+    ap.add_argument("--kernels-alone", action="store_true",
+                    help="with --designs: only the talking attention and the gated recurrence, each alone (a small case)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -770,7 +839,7 @@ def main():
         return 2
     args.warmup = max(3, args.warmup)
     if args.designs:
-        return run_designs(args)
+        return time_design_kernels(args) if args.kernels_alone else run_designs(args)
     return run_ours(args)
 
 

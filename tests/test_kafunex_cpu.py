@@ -211,3 +211,20 @@ def test_greedy_generation_through_the_scheduler(models):
         assert o == P.greedy(cfg, w, p, 20)
     eng.runner.cache.check()
     assert eng.runner.cache.num_free_slots == 4
+
+
+def test_the_new_parts_in_another_arrangement():
+    """The attention part with values of its own and without head mixing, gate, norms, distance bias or chunk rule, and the
+    feed-forward with another activation, in a post-norm block behind a plain embedding: what a different design would
+    put together from the same descriptions.  Compared with the formulas written out in tiny_kafunex.another_arrangement."""
+    from infurnace_b200.engine.runner import ModelRunner, StepEntry
+    from infurnace_b200.parts import DecoderModel, Runtime
+    plan, w, toks, want = TK.another_arrangement()
+    assert set(plan.tensors()) == set(w)
+    rt = Runtime(device=torch.device("cpu"), act_dtype=torch.float32, kernels=ReferenceKernels(torch.float64))
+    cache = CacheManager(plan, page_size=4, num_pages=16, max_requests=2, dtype=torch.float32, device="cpu")
+    runner = ModelRunner(DecoderModel(plan, w, rt), cache, rt, 64, 64)
+    cache.add_request("a")
+    got = torch.cat([runner.step([StepEntry("a", toks[:13], list(range(13)))]).clone(),
+                     runner.step([StepEntry("a", toks[13:], list(range(len(toks) - 13)))]).clone()]).double()
+    assert (got - want).abs().max() < TOL

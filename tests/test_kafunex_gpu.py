@@ -393,3 +393,23 @@ def test_command_line_and_random_weights(models, tmp_path):
                           "--json"], capture_output=True, text=True, timeout=600, cwd=root)
     assert out.returncode == 0, out.stderr
     assert len(json.loads(out.stdout)["generated_token_ids"]) == 5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_new_parts_in_another_arrangement(dtype):
+    """A plain embedding (the block makes the stream's bfloat16 copy itself), attention with values of its own and none of
+    the options, a gelu feed-forward: on the GPU kernels, a prompt portion and then single tokens."""
+    from infurnace_b200.cache import CacheManager
+    from infurnace_b200.engine.runner import ModelRunner, StepEntry
+    from infurnace_b200.kernels import load_cuda_kernels
+    from infurnace_b200.parts import DecoderModel, Runtime
+    plan, w, toks, want = TK.another_arrangement()
+    dev = torch.device("cuda")
+    rt = Runtime(device=dev, act_dtype=dtype, kernels=load_cuda_kernels())
+    cache = CacheManager(plan, page_size=4, num_pages=16, max_requests=2, dtype=dtype, device=dev)
+    runner = ModelRunner(DecoderModel(plan, {k: v.to(dev, dtype) for k, v in w.items()}, rt), cache, rt, 64, 64)
+    cache.add_request("a")
+    got = [runner.step([StepEntry("a", toks[:13], list(range(13)))]).float().cpu().clone()]
+    got += [runner.step([StepEntry("a", [t], [0])]).float().cpu().clone() for t in toks[13:]]
+    err = float((torch.cat(got).double() - want).abs().max())
+    assert err <= (F32_TOL if dtype == torch.float32 else bf16_tol([want])), err

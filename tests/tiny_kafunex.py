@@ -91,3 +91,43 @@ def make_model_dir(name, root):
     save_file({k: v.to(dt).contiguous() for k, v in make_weights(spec["config"], spec["seed"]).items()},
               os.path.join(d, "model.safetensors"))
     return d
+
+
+def another_arrangement():
+    """(plan, weights, tokens, logits written out in float64) of a one-layer model put together from the same part
+    descriptions in another way: a plain embedding, attention with a value projection of its own and nothing else
+    (no norms, no mixing of heads, no gate, no distance bias, no chunk rule), a gelu feed-forward, post-norm block."""
+    import math
+    from infurnace_b200.config.specs import (DenseMLPSpec, EmbeddingSpec, LayerCall, LMHeadSpec, ModelPlan, PostNormBlockSpec,
+                                             ScalarRMSNormSpec, TalkingAttentionSpec)
+    W, H, G, d, V, F, T = 24, 4, 2, 8, 40, 24, 21
+    g = torch.Generator().manual_seed(4)
+    bf = lambda t: t.to(torch.bfloat16).float()          # values a bfloat16 engine holds exactly
+    w = {"emb": bf(torch.randn(V, W, generator=g)), "q": bf(torch.randn(H * d, W, generator=g) / 3),
+         "k": bf(torch.randn(G * d, W, generator=g) / 3), "v": bf(torch.randn(G * d, W, generator=g) / 3),
+         "o": bf(torch.randn(W, H * d, generator=g) / 3), "n1": bf(torch.tensor(1.2)), "s1": bf(1 + 0.2 * torch.randn(W, generator=g)),
+         "up": bf(torch.randn(F, W, generator=g) / 3), "down": bf(torch.randn(W, F, generator=g) / 3), "n2": bf(torch.tensor(0.8)),
+         "s2": bf(1 + 0.2 * torch.randn(W, generator=g)), "nf": bf(torch.tensor(1.1)), "head": bf(torch.randn(V, W, generator=g) / 3)}
+    attn = TalkingAttentionSpec(hidden_size=W, num_heads=H, num_kv_heads=G, head_dim=d, scale=0.7, eps=1e-5, q_proj="q", k_proj="k",
+                                o_proj="o", v_proj="v", slope_exponent=None)
+    block = PostNormBlockSpec(W, attn, ScalarRMSNormSpec(1e-5, "n1"), "s1", DenseMLPSpec(W, F, "gelu_tanh", "up", "down"),
+                              ScalarRMSNormSpec(1e-5, "n2"), "s2")
+    plan = ModelPlan("other", V, W, 256, EmbeddingSpec(V, W, "emb"), (block,), (LayerCall(0),), ScalarRMSNormSpec(1e-5, "nf"),
+                     LMHeadSpec(V, W, "head", tied=False))
+    toks = [int(t) for t in torch.randint(0, V, (T,), generator=g)]
+    D = torch.float64
+
+    def rms(t):
+        return t / torch.sqrt(t.pow(2).mean(-1, keepdim=True) + 1e-5)
+
+    x = w["emb"].to(D)[torch.tensor(toks)]
+    q, k, v = (x @ w[n].to(D).t() for n in ("q", "k", "v"))
+    q, k, v = q.view(T, H, d), k.view(T, G, d).repeat_interleave(H // G, 1), v.view(T, G, d).repeat_interleave(H // G, 1)
+    a = torch.einsum("thd,shd->hts", q, k) * 0.7
+    a = a.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool))[None], float("-inf"))
+    y = torch.einsum("hts,shd->thd", torch.softmax(a, -1), v).reshape(T, H * d) @ w["o"].to(D).t()
+    x = x + rms(y) * w["n1"].to(D) * w["s1"].to(D)
+    z = x @ w["up"].to(D).t()
+    y = (0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))) @ w["down"].to(D).t()
+    x = x + rms(y) * w["n2"].to(D) * w["s2"].to(D)
+    return plan, w, toks, (rms(x) * w["nf"].to(D)) @ w["head"].to(D).t()

@@ -83,18 +83,26 @@ class CacheLayout:
         self.state: Dict[tuple, Tuple[StateNeed, List[int]]] = {}
         self.group_of: Dict[int, tuple] = {}
         for call in plan.resolved_schedule():
-            need = plan.layers[call.layer].cache_need()
-            if need is None:
-                continue
-            key = need.group_key
-            if call.cache in self.group_of:
-                if self.group_of[call.cache] != key:
-                    raise CacheError(f"cache entry {call.cache} is read by a layer with a different need "
-                                     f"({key}) than the layer that stores it ({self.group_of[call.cache]})")
-                continue
-            self.group_of[call.cache] = key
-            table = self.kv if isinstance(need, (KVCacheNeed, PagedCacheNeed)) else self.state
-            table.setdefault(key, (need, []))[1].append(call.cache)
+            self._enter(call.cache, plan.layers[call.layer].cache_need())
+
+    def _enter(self, cache_id, need) -> None:
+        """One cache entry; a tuple of needs (a mixer made of several, a mixer with two kinds of state) gives
+        entry j the id ``(cache_id, j)``."""
+        if need is None:
+            return
+        if isinstance(need, tuple):
+            for j, sub in enumerate(need):
+                self._enter((cache_id, j), sub)
+            return
+        key = need.group_key
+        if cache_id in self.group_of:
+            if self.group_of[cache_id] != key:
+                raise CacheError(f"cache entry {cache_id} is read by a layer with a different need "
+                                 f"({key}) than the layer that stores it ({self.group_of[cache_id]})")
+            return
+        self.group_of[cache_id] = key
+        table = self.kv if isinstance(need, (KVCacheNeed, PagedCacheNeed)) else self.state
+        table.setdefault(key, (need, []))[1].append(cache_id)
 
 
 class CacheManager:

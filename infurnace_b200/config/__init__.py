@@ -3,6 +3,9 @@ from .specs import (  # noqa: F401
     TensorSpec, KVCacheNeed, StateNeed, RMSNormSpec, RotarySpec, AttentionSpec, GatedMLPSpec,
     PreNormBlockSpec, EmbeddingSpec, LMHeadSpec, LayerCall, ModelPlan,
     ScalarRMSNormSpec, SinusoidEmbeddingSpec, DenseMLPSpec, GatedRecurrenceSpec, TalkingAttentionSpec, PostNormBlockSpec,
+    NormedEmbeddingSpec, StreamInjectSpec, RetentionSpec, TimeMixSpec, GatedUnitSpec, RotaryValueAttentionSpec,
+    ParallelMixerSpec, RoutedExpertsSpec, TokenSideSpec, SandwichBlockSpec,
 )
 from .qwen3 import Qwen3Config  # noqa: F401
 from .kafunex import KafunexConfig  # noqa: F401
+from .lunelorn import LunelornConfig  # noqa: F401

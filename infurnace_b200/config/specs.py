@@ -30,10 +30,13 @@ class TensorSpec:
     """One tensor of a model folder.  ``kind`` is "float" (kept in the engine's weight
     dtype, see weights/loader.py) or "int" (an integer table, kept as int32).  ``init``:
     (mean, standard deviation) of the tensor in random-weights mode, where its shape alone
-    would give the wrong idea (a single number that is a norm weight, a lower bound in (0, 1))."""
-    shape: Tuple[int, ...]
+    would give the wrong idea (a single number that is a norm weight, a lower bound in (0, 1)).  An entry of
+    ``shape`` may be None: the file gives that size (the part reads it from the tensor).  ``optional``: a folder
+    may hold the tensor or not; no part needs it."""
+    shape: Tuple[Optional[int], ...]
     kind: str = "float"
     init: Optional[Tuple[float, float]] = None
+    optional: bool = False
 
 
 # --------------------------------------------------------------------------- cache needs
@@ -226,6 +229,7 @@ class LMHeadSpec:
     weight: str
     tied: bool
     stored_as: Optional[str] = None
+    softcap: Optional[float] = None       # c: logits <- c * tanh(logits / c)
 
     def tensors(self) -> Mapping[str, TensorSpec]:
         if self.tied:
@@ -390,6 +394,258 @@ class PostNormBlockSpec:
         return self.mixer.cache_need()
 
 
+# --------------------------------------------------------------------------- parts of sandwich-norm hybrid decoders
+@dataclass(frozen=True)
+class NormedEmbeddingSpec:
+    """x[t] = norm(table[id_t]).  ``keep``: the rows are also kept for the step (a later part adds them to the
+    stream again, see :class:`StreamInjectSpec`)."""
+    vocab_size: int
+    hidden_size: int
+    weight: str
+    norm: object
+    keep: bool = False
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        return {self.weight: TensorSpec((self.vocab_size, self.hidden_size)), **self.norm.tensors()}
+
+
+@dataclass(frozen=True)
+class StreamInjectSpec:
+    """A step between layers that only adds to the stream: x += row ``row`` of the table ``table`` [rows, width]
+    (one vector for all tokens), and, with ``add_embedding``, the rows the embedding kept.  It stands in the
+    schedule like a layer and keeps nothing in the cache."""
+    hidden_size: int
+    table: str
+    rows: int
+    row: int
+    add_embedding: bool = False
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        return {self.table: TensorSpec((self.rows, self.hidden_size), init=(0.0, 0.3))}
+
+    def cache_need(self):
+        return None
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with one fixed decay per head, no softmax and no denominator.  Per head a float32 state
+    S [dim, vdim], zero at the start of a sequence: S <- decay_h S + (k * key_scale) v^T, o = S^T q.  Each head's o
+    is divided by its root mean square (no weight), the heads side by side are multiplied by silu(G h) and go
+    through ``o_proj``."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    value_head_dim: int
+    decay: Tuple[float, ...]
+    key_scale: float
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    g_proj: str
+    o_proj: str
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        hd, hv = self.num_heads * self.head_dim, self.num_heads * self.value_head_dim
+        return {self.q_proj: TensorSpec((hd, self.hidden_size)), self.k_proj: TensorSpec((hd, self.hidden_size)),
+                self.v_proj: TensorSpec((hv, self.hidden_size)), self.g_proj: TensorSpec((hv, self.hidden_size)),
+                self.o_proj: TensorSpec((self.hidden_size, hv))}
+
+    def cache_need(self):
+        return StateNeed((self.num_heads, self.head_dim, self.value_head_dim))
+
+
+@dataclass(frozen=True)
+class TimeMixSpec:
+    """RWKV-style time mixing.  With h' the previous token's input (zeros before the first), each of r, k, v, g, w
+    reads its own blend h + (h' - h) * mu_s.  Per head a float32 state S [dim, dim]: the decay is
+    w = exp(-exp(W2 tanh(W1 mix_w) + w0)) per token, head and key channel; o = (S + diag(u) k v^T)^T r (the bonus u
+    for the current token only), then S <- diag(w) S + k v^T.  Each head's o is divided by its root mean square,
+    times ``out_norm`` (per head and channel), times silu(G mix_g), then ``o_proj``.  The previous token's input is
+    part of the state.  ``rank`` (the width of the decay's bottleneck) None: the stored tensors give it."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    eps: float
+    mu: Tuple[str, str, str, str, str]        # the blends of r, k, v, g, w
+    r_proj: str
+    k_proj: str
+    v_proj: str
+    g_proj: str
+    w1: str
+    w2: str
+    w0: str
+    bonus: str
+    out_norm: str
+    o_proj: str
+    rank: Optional[int] = None
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        hd, W = self.num_heads * self.head_dim, self.hidden_size
+        t = {name: TensorSpec((W,), init=(0.5, 0.25)) for name in self.mu}
+        for name in (self.r_proj, self.k_proj, self.v_proj, self.g_proj):
+            t[name] = TensorSpec((hd, W))
+        t[self.w1] = TensorSpec((self.rank, W))
+        t[self.w2] = TensorSpec((hd, self.rank))
+        t[self.w0] = TensorSpec((hd,), init=(-1.5, 1.0))
+        t[self.bonus] = TensorSpec((self.num_heads, self.head_dim), init=(0.3, 0.3))
+        t[self.out_norm] = TensorSpec((hd,))
+        t[self.o_proj] = TensorSpec((W, hd))
+        return t
+
+    def cache_need(self):
+        return (StateNeed((self.num_heads, self.head_dim, self.head_dim)), StateNeed((self.hidden_size,)))
+
+
+@dataclass(frozen=True)
+class GatedUnitSpec:
+    """minGRU: an element-wise gated recurrence whose gates read only the current token.  z = sigmoid(Z h + bz),
+    u = X h + bx, candidate = u + 1/2 where u >= 0 and sigmoid(u) where u < 0; S <- (1 - z) S + z * candidate per
+    element of a float32 state [width]; the output is ``o_proj``(S * silu(G h))."""
+    hidden_size: int
+    width: int
+    z_proj: str
+    z_bias: str
+    x_proj: str
+    x_bias: str
+    g_proj: str
+    o_proj: str
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        n, W = self.width, self.hidden_size
+        return {self.z_proj: TensorSpec((n, W)), self.z_bias: TensorSpec((n,), init=(0.0, 0.5)),
+                self.x_proj: TensorSpec((n, W)), self.x_bias: TensorSpec((n,), init=(0.0, 0.5)),
+                self.g_proj: TensorSpec((n, W)), self.o_proj: TensorSpec((W, n))}
+
+    def cache_need(self):
+        return StateNeed((self.width,))
+
+
+@dataclass(frozen=True)
+class RotaryValueAttentionSpec:
+    """Grouped-query softmax attention whose values carry positions too.  q and k are rotated on their first
+    ``position.rotary_dim`` entries (:class:`RotarySpec`).  ``value_norm``: each value head is divided by its root
+    mean square (no weight) before it is cached.  ``value_position``: the value of position j is rotated by j over
+    that description's width before it is cached, and each head's summed output at position i is rotated back by
+    -i.  Causal, optional window, plain softmax; key and value heads may differ in width."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_head_dim: int
+    scale: float
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    o_proj: str
+    position: Optional[RotarySpec] = None
+    value_norm: bool = False
+    value_position: Optional[RotarySpec] = None
+    window: Optional[int] = None
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        W = self.hidden_size
+        return {self.q_proj: TensorSpec((self.num_heads * self.head_dim, W)),
+                self.k_proj: TensorSpec((self.num_kv_heads * self.head_dim, W)),
+                self.v_proj: TensorSpec((self.num_kv_heads * self.value_head_dim, W)),
+                self.o_proj: TensorSpec((W, self.num_heads * self.value_head_dim))}
+
+    def cache_need(self):
+        return KVCacheNeed(self.num_kv_heads, self.head_dim, self.window,
+                           None if self.value_head_dim == self.head_dim else self.value_head_dim)
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side that read the same input; the result is the sum of ``scales[i] * mixers[i](h)``.
+    Each keeps its own cache entry (``cache_need`` is the tuple of theirs)."""
+    mixers: Tuple[object, ...]
+    scales: Tuple[float, ...]
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        t = {}
+        for m in self.mixers:
+            t.update(m.tensors())
+        return t
+
+    def cache_need(self):
+        return tuple(m.cache_need() for m in self.mixers)
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of gated feed-forwards without biases.  Router logits z = R h in 32-bit; each token runs the
+    ``top`` experts with the largest logits, weighted by the softmax over those logits only; an expert is
+    down(act(gate h) * (up h)).  ``experts`` names each expert's (gate, up, down) tensors."""
+    hidden_size: int
+    intermediate_size: int
+    top: int
+    activation: str
+    router: str
+    experts: Tuple[Tuple[str, str, str], ...]
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        t = {self.router: TensorSpec((len(self.experts), self.hidden_size), init=(0.0, 0.3))}
+        for gate, up, down in self.experts:
+            t[gate] = TensorSpec((self.intermediate_size, self.hidden_size))
+            t[up] = TensorSpec((self.intermediate_size, self.hidden_size))
+            t[down] = TensorSpec((self.hidden_size, self.intermediate_size))
+        return t
+
+    def cache_need(self):
+        return None
+
+
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A per-layer token input: e = columns ``offset`` .. ``offset + dim`` of row id_t of ``table``;
+    g = act(``gate`` x) * e; y = ``proj`` g; x += y / rms(y) * ``norm``."""
+    hidden_size: int
+    dim: int
+    vocab_size: int
+    table: str
+    table_width: int
+    offset: int
+    activation: str
+    gate: str
+    proj: str
+    norm: RMSNormSpec
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        return {self.table: TensorSpec((self.vocab_size, self.table_width)), self.gate: TensorSpec((self.dim, self.hidden_size)),
+                self.proj: TensorSpec((self.hidden_size, self.dim)), **self.norm.tensors()}
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """x += post1(mixer(pre1(x))); x += post2(ffn(pre2(x))); then the token side input, if any.  A norm stands
+    before and after each sublayer.  ``ffn`` None: no feed-forward; its norms may then still be stored
+    (``unused``: tensors a folder may hold that no part reads)."""
+    hidden_size: int
+    mixer_norm: object
+    mixer: object
+    mixer_post_norm: object
+    ffn_norm: Optional[object] = None
+    ffn: Optional[object] = None
+    ffn_post_norm: Optional[object] = None
+    side: Optional[TokenSideSpec] = None
+    unused: Tuple[str, ...] = ()
+
+    def tensors(self) -> Mapping[str, TensorSpec]:
+        t = {}
+        for part in (self.mixer_norm, self.mixer, self.mixer_post_norm, self.ffn_norm, self.ffn, self.ffn_post_norm, self.side):
+            if part is not None:
+                t.update(part.tensors())
+        for name in self.unused:
+            t.setdefault(name, TensorSpec((self.hidden_size,), optional=True))
+        return t
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+
 # --------------------------------------------------------------------------- the order
 @dataclass(frozen=True)
 class LayerCall:
@@ -400,7 +656,7 @@ class LayerCall:
     cache of its own) and a call may name another call's cache id with ``store`` False:
     then it reads what that call stored and stores nothing itself."""
     layer: int
-    cache: Optional[int] = None
+    cache: Optional[object] = None       # an int; parts that keep several entries derive (cache, j) for entry j
     store: bool = True
 
 

@@ -103,6 +103,7 @@ class StepContext:
         self.num_requests = 0
         self.num_logit_rows = 0
         self.max_logit_rows = runner.max_tokens
+        self.max_rows = runner._n_cap               # the most rows of the flat token axis that a step can have
         self.max_q_len = 0
         self.min_q_len = 1
         self.max_seq_len = 0

@@ -6,3 +6,4 @@ from .registry import (  # noqa: F401
 )
 from . import qwen3  # noqa: F401  (registers "Qwen3ForCausalLM")
 from . import kafunex  # noqa: F401  (registers "Kafunex")
+from . import lunelorn  # noqa: F401  (registers "Lunelorn")

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import PostNormBlockSpec, PreNormBlockSpec
+from ..config.specs import PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec, StreamInjectSpec, TokenSideSpec
 from .registry import Folded, build_part, register_part
 
 
@@ -115,3 +115,117 @@ class PostNormBlock:
 
 
 register_part(PostNormBlockSpec, PostNormBlock)
+
+
+class TokenSide:
+    """x += norm(proj(act(gate x) * e)) with e a slice of the token's row of a table shared by the layers.  ``xa`` is
+    the stream in the dtype the products read.  The gate product writes float32; one kernel applies the activation
+    and the token's slice; the stream's update is the block's update kernel."""
+
+    graph_safe = True
+
+    def __init__(self, spec: TokenSideSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.table = weights[spec.table]
+        self.w_gate, self.w_proj = weights[spec.gate], weights[spec.proj]
+        self.norm = build_part(spec.norm, weights, runtime)
+
+    def forward(self, xa, ctx):
+        s, k = self.spec, self.k
+        n = xa.shape[0]
+        z = ctx.buffer("side_z", (n, s.dim), torch.float32)
+        k.linear(xa, self.w_gate, z)
+        g = ctx.buffer("side_g", (n, s.dim), self.rt.act_dtype)
+        k.token_side_gate(z, self.table, ctx.token_ids, s.offset, s.activation, g)
+        y = ctx.buffer("delta_side", (n, s.hidden_size), torch.float32)
+        k.linear(g, self.w_proj, y)
+        return y
+
+
+register_part(TokenSideSpec, TokenSide)
+
+
+class SandwichBlock:
+    """x += post1(mixer(pre1(x))); x += post2(ffn(pre2(x))); then the token side input.  Every update of the stream
+    is one kernel that normalises the sublayer's float32 result, adds it to x in float32 and, in the same pass, writes
+    what the next product reads: the next pre-norm of x, or x itself in the products' dtype.  x is up to date when the
+    block returns; it hands on no pending delta."""
+
+    def __init__(self, spec: SandwichBlockSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.mixer_norm = build_part(spec.mixer_norm, weights, runtime)
+        self.mixer = build_part(spec.mixer, weights, runtime)
+        self.mixer_post = build_part(spec.mixer_post_norm, weights, runtime)
+        self.ffn = build_part(spec.ffn, weights, runtime) if spec.ffn is not None else None
+        self.ffn_norm = build_part(spec.ffn_norm, weights, runtime) if spec.ffn is not None else None
+        self.ffn_post = build_part(spec.ffn_post_norm, weights, runtime) if spec.ffn is not None else None
+        self.side = build_part(spec.side, weights, runtime) if spec.side is not None else None
+
+    @property
+    def graph_safe(self):
+        parts = [self.mixer] + [p for p in (self.ffn, self.side) if p is not None]
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
+    def _update(self, x, y, post, ctx, then_norm=None, then_copy=False):
+        """x += y / rms(y) * post.weight; returns the next product's input if one was asked for."""
+        out = None
+        if then_norm is not None or then_copy:
+            out = ctx.buffer("h", x.shape, self.rt.act_dtype)
+        self.k.residual_norm_update(x, y, post.weight, post.spec.eps, out=out,
+                                    next_weight=then_norm.weight if then_norm is not None else None)
+        return out
+
+    def forward(self, x, pending, ctx, call):
+        if pending is not None:                      # a block of another kind ran before and left its last delta
+            if isinstance(pending, Folded):
+                raise TypeError("a sandwich block cannot take a folded norm from the block before it")
+            x.add_(pending)
+        h = ctx.buffer("h", x.shape, self.rt.act_dtype)
+        self.mixer_norm.forward(x, h)
+        y = self.mixer.forward(h, ctx, call)
+        if self.ffn is not None:
+            h = self._update(x, y, self.mixer_post, ctx, then_norm=self.ffn_norm)
+            y = self.ffn.forward(h, ctx)
+            xa = self._update(x, y, self.ffn_post, ctx, then_copy=self.side is not None)
+        else:
+            xa = self._update(x, y, self.mixer_post, ctx, then_copy=self.side is not None)
+        if self.side is not None:
+            self._update(x, self.side.forward(xa, ctx), self.side.norm, ctx)
+        return None
+
+
+register_part(SandwichBlockSpec, SandwichBlock)
+
+
+class StreamInject:
+    """x += table[row] (+ the rows the embedding kept): the step that opens a pass over a range of layers that runs
+    several times.  It stands in the schedule like a layer."""
+
+    graph_safe = True
+
+    def __init__(self, spec: StreamInjectSpec, weights, runtime):
+        from .model import EMBEDDING_ROWS
+        self.spec = spec
+        self.k = runtime.kernels
+        self.vec = weights[spec.table][spec.row].contiguous()
+        self._key = EMBEDDING_ROWS
+
+    def forward(self, x, pending, ctx, call):
+        if pending is not None:
+            if isinstance(pending, Folded):
+                raise TypeError("an injection step cannot take a folded norm from the block before it")
+            x.add_(pending)
+        rows = None
+        if self.spec.add_embedding:
+            rows = ctx.shared.get(self._key)
+            if rows is None:
+                raise RuntimeError("the embedding kept no rows for this step (its description needs keep=True)")
+        self.k.add_rows(x, rows, self.vec)
+        return None
+
+
+register_part(StreamInjectSpec, StreamInject)

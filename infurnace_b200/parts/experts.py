@@ -1,0 +1,55 @@
+"""A mixture of gated feed-forwards."""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import RoutedExpertsSpec
+from ..errors import ModelConfigError
+from .registry import register_part
+
+
+class RoutedExperts:
+    """h -> sum over a token's ``top`` experts of weight * down_e(act(gate_e h) * up_e h).
+
+    The router's logits are a product into float32.  One kernel picks each token's ``top`` largest logits and takes
+    the softmax over them; one lists, per expert, the (token, choice) pairs that chose it, in token order (all on the
+    device: the step's launches depend on its sizes only).  The experts' products then run as two grouped launches
+    over that list (gate | up with the activation in the epilogue, then down) against the experts' matrices stacked
+    along a leading axis, and one kernel sums each token's results in the order of its choices, in float32."""
+
+    graph_safe = True
+
+    def __init__(self, spec: RoutedExpertsSpec, weights, runtime):
+        if spec.activation != "silu":
+            raise ModelConfigError(f"activation {spec.activation!r}: only 'silu' has a kernel")
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.router = weights[spec.router]
+        self.w_gate_up = torch.stack([torch.cat((weights[g], weights[u]), dim=0) for g, u, _ in spec.experts], dim=0).contiguous()
+        self.w_down = torch.stack([weights[d] for _, _, d in spec.experts], dim=0).contiguous()
+        self.num_experts = len(spec.experts)
+
+    def forward(self, h, ctx, fold=None):
+        s, k, E = self.spec, self.k, self.num_experts
+        n = h.shape[0]
+        logits = ctx.buffer("moe_logits", (n, E), torch.float32)
+        k.linear(h, self.router, logits)
+        ids = ctx.buffer("moe_ids", (n, s.top), torch.int32)
+        gates = ctx.buffer("moe_gates", (n, s.top), torch.float32)
+        k.moe_route(logits, s.top, ids, gates)
+        pairs = n * s.top
+        offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32, rows=E + 1)
+        perm = ctx.buffer("moe_perm", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
+        pos = ctx.buffer("moe_pos", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
+        k.moe_plan(ids, E, offsets, perm, pos)
+        act = ctx.buffer("moe_act", (pairs, s.intermediate_size), self.rt.act_dtype, rows=ctx.max_rows * s.top)
+        k.moe_linear(h, self.w_gate_up, offsets, perm, s.top, act, epilogue="silu_gate")
+        y = ctx.buffer("moe_y", (pairs, s.hidden_size), torch.float32, rows=ctx.max_rows * s.top)
+        k.moe_linear(act, self.w_down, offsets, None, 1, y)
+        delta = ctx.buffer("delta_ffn", (n, s.hidden_size), torch.float32)
+        k.moe_combine(y, pos, gates, delta)
+        return delta
+
+
+register_part(RoutedExpertsSpec, RoutedExperts)

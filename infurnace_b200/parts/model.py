@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..config.specs import EmbeddingSpec, LMHeadSpec, ModelPlan, SinusoidEmbeddingSpec
+from ..config.specs import EmbeddingSpec, LMHeadSpec, ModelPlan, NormedEmbeddingSpec, SinusoidEmbeddingSpec
 from .registry import build_part, register_part
 
 
@@ -32,6 +32,8 @@ class LMHead:
 
     def forward(self, h, out):
         self.k.linear(h, self.weight, out)
+        if self.spec.softcap:                  # c * tanh(logits / c), in place
+            self.k.softcap(out, float(self.spec.softcap))
         return out
 
 
@@ -61,6 +63,33 @@ class SinusoidEmbedding:
         return out
 
 
+class NormedEmbedding:
+    """x[t] = norm(table[id_t]) in float32: the gather writes a scratch buffer and the norm kernel writes the stream.
+    With ``keep`` the rows are also copied to a buffer of the step (``ctx.shared[EMBEDDING_ROWS]``) for a later part
+    that adds them to the stream again."""
+
+    uses_context = True
+
+    def __init__(self, spec: NormedEmbeddingSpec, weights, runtime):
+        self.spec = spec
+        self.table = weights[spec.weight]
+        self.norm = build_part(spec.norm, weights, runtime)
+        self.k = runtime.kernels
+
+    def forward(self, ids, out, ctx=None):
+        raw = ctx.buffer("embed_raw", out.shape, torch.float32)
+        self.k.embed(self.table, ids, raw)
+        self.norm.forward(raw, out)
+        if self.spec.keep:
+            kept = ctx.buffer("embed_kept", out.shape, torch.float32)
+            self.k.add_rows(kept, out, None, accumulate=False)
+            ctx.shared[EMBEDDING_ROWS] = kept
+        return out
+
+
+# key of ``ctx.shared`` under which the embedding's rows are kept for the step
+EMBEDDING_ROWS = ("embedding_rows",)
+
 # key of ``ctx.shared`` under which a bfloat16 copy of the current residual stream is handed from the part that wrote the
 # stream last (an embedding, a block's residual update) to the part that reads it next
 STREAM_COPY = ("stream_copy",)
@@ -68,6 +97,7 @@ STREAM_COPY = ("stream_copy",)
 register_part(EmbeddingSpec, Embedding)
 register_part(SinusoidEmbeddingSpec, SinusoidEmbedding)
 register_part(LMHeadSpec, LMHead)
+register_part(NormedEmbeddingSpec, NormedEmbedding)
 
 
 class DecoderModel:

@@ -1,9 +1,10 @@
-"""The HGRN2 mixer: a gated linear recurrence with a matrix state per head in the request's state slot."""
+"""Recurrent mixers whose state lives in the request's state slot: the HGRN2 gated recurrence, retention with a fixed
+decay per head, RWKV-style time mixing (all three a matrix state per head) and the element-wise minGRU."""
 from __future__ import annotations
 
 import torch
 
-from ..config.specs import GatedRecurrenceSpec
+from ..config.specs import GatedRecurrenceSpec, GatedUnitSpec, RetentionSpec, TimeMixSpec
 from .registry import register_part
 
 
@@ -46,3 +47,116 @@ class GatedRecurrence:
 
 
 register_part(GatedRecurrenceSpec, GatedRecurrence)
+
+
+class Retention:
+    """h -> o_proj(unit_norm(S^T q) * silu(G h)) with S <- decay_h S + (k * key_scale) v^T per head.
+
+    q | k | v | g run as one product into float32 (what enters the recurrence is 32-bit).  The recurrence kernel is
+    the framework's walk of a matrix state per head (``linear_scan``) with a constant decay per head; it divides each
+    head's output by its root mean square and multiplies by silu of the gate columns before it writes the rows that
+    ``o_proj`` reads.  A prompt, a portion and a decoded token are the same call: the slot's state carries the past."""
+
+    graph_safe = True
+
+    def __init__(self, spec: RetentionSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.w_all = torch.cat([weights[n] for n in (spec.q_proj, spec.k_proj, spec.v_proj, spec.g_proj)], dim=0).contiguous()
+        self.w_o = weights[spec.o_proj]
+        self.decay = torch.tensor(spec.decay, dtype=torch.float32, device=runtime.device)
+        self.hd = spec.num_heads * spec.head_dim
+        self.hv = spec.num_heads * spec.value_head_dim
+
+    def forward(self, h, ctx, call):
+        s, k, hd, hv = self.spec, self.k, self.hd, self.hv
+        n = h.shape[0]
+        proj = ctx.buffer("ret_proj", (n, 2 * hd + 2 * hv), torch.float32)
+        k.linear(h, self.w_all, proj)
+        out = ctx.buffer("ret_out", (n, hv), self.rt.act_dtype)
+        k.linear_scan(proj[:, :hd], proj[:, hd:2 * hd], proj[:, 2 * hd:2 * hd + hv], None, s.num_heads, s.head_dim,
+                      s.value_head_dim, ctx.state(call.cache), ctx.state_slots, ctx.cu_q, ctx.seq_lens, out, s.eps,
+                      decay=self.decay, key_scale=s.key_scale, gate=proj[:, 2 * hd + hv:], max_q_len=ctx.max_q_len)
+        delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
+        k.linear(out, self.w_o, delta)
+        return delta
+
+
+register_part(RetentionSpec, Retention)
+
+
+class TimeMix:
+    """RWKV-style time mixing over two cache entries: the matrix state per head, and the previous token's input.
+
+    One kernel forms the five blends of each token with the one before it (the slot's saved row for the first token
+    of a step) and saves the step's last row.  r, k, v, g and the decay's bottleneck read their blends through the
+    framework's products (into float32; the bottleneck's tanh is its product's epilogue); the recurrence kernel
+    turns the raw decay into exp(-exp(. + w0)), reads each output from the state BEFORE the token's update with the
+    bonus on the token's own k v^T, and finishes with the per-head unit norm, the stored norm weight and the gate."""
+
+    graph_safe = True
+
+    def __init__(self, spec: TimeMixSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.mu = torch.stack([weights[n].to(torch.float32) for n in spec.mu], dim=0).contiguous()
+        self.w_r, self.w_k, self.w_v, self.w_g = (weights[n] for n in (spec.r_proj, spec.k_proj, spec.v_proj, spec.g_proj))
+        self.w1, self.w2, self.w0 = weights[spec.w1], weights[spec.w2], weights[spec.w0]
+        self.rank = self.w1.shape[0]
+        self.bonus = weights[spec.bonus].reshape(-1).contiguous()
+        self.norm_w = weights[spec.out_norm]
+        self.w_o = weights[spec.o_proj]
+        self.hd = spec.num_heads * spec.head_dim
+
+    def forward(self, h, ctx, call):
+        s, k, hd = self.spec, self.k, self.hd
+        n, W = h.shape
+        mixes = ctx.buffer("tm_mixes", (5 * n, W), self.rt.act_dtype).view(5, n, W)
+        k.token_shift_mix(h, ctx.state((call.cache, 1)), ctx.state_slots, ctx.cu_q, ctx.seq_lens, self.mu, mixes)
+        proj = [ctx.buffer("tm_" + name, (n, hd), torch.float32) for name in ("r", "k", "v", "g", "w")]
+        for j, w in enumerate((self.w_r, self.w_k, self.w_v, self.w_g)):
+            k.linear(mixes[j], w, proj[j])
+        low = ctx.buffer("tm_low", (n, self.rank), self.rt.act_dtype)
+        k.linear(mixes[4], self.w1, low, epilogue="tanh")
+        k.linear(low, self.w2, proj[4])
+        out = ctx.buffer("tm_out", (n, hd), self.rt.act_dtype)
+        k.linear_scan(proj[0], proj[1], proj[2], proj[4], s.num_heads, s.head_dim, s.head_dim, ctx.state((call.cache, 0)),
+                      ctx.state_slots, ctx.cu_q, ctx.seq_lens, out, s.eps, w_bias=self.w0, bonus=self.bonus,
+                      norm_weight=self.norm_w, gate=proj[3], max_q_len=ctx.max_q_len)
+        delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
+        k.linear(out, self.w_o, delta)
+        return delta
+
+
+register_part(TimeMixSpec, TimeMix)
+
+
+class GatedUnit:
+    """minGRU: z | x | g run as one product into float32; one kernel adds the biases, forms gate and candidate,
+    walks each request's tokens element by element from the slot's state and writes S * silu(g)."""
+
+    graph_safe = True
+
+    def __init__(self, spec: GatedUnitSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.w_all = torch.cat([weights[n] for n in (spec.z_proj, spec.x_proj, spec.g_proj)], dim=0).contiguous()
+        self.z_bias, self.x_bias = weights[spec.z_bias], weights[spec.x_bias]
+        self.w_o = weights[spec.o_proj]
+
+    def forward(self, h, ctx, call):
+        s, k = self.spec, self.k
+        n = h.shape[0]
+        proj = ctx.buffer("gu_proj", (n, 3 * s.width), torch.float32)
+        k.linear(h, self.w_all, proj)
+        out = ctx.buffer("gu_out", (n, s.width), self.rt.act_dtype)
+        k.gated_unit_scan(proj, self.z_bias, self.x_bias, ctx.state(call.cache), ctx.state_slots, ctx.cu_q, ctx.seq_lens, out)
+        delta = ctx.buffer("delta_unit", (n, s.hidden_size), torch.float32)
+        k.linear(out, self.w_o, delta)
+        return delta
+
+
+register_part(GatedUnitSpec, GatedUnit)

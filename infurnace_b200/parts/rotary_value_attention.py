@@ -1,0 +1,60 @@
+"""Softmax attention over the paged cache whose values are normalised and rotated by their position."""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import RotaryValueAttentionSpec
+from .registry import build_part, register_part
+
+
+class RotaryValueAttention:
+    """h -> o_proj(unrotate(attention(q, K, V))).
+
+    q | k | v run as one product.  One kernel rotates the q and k heads on their first rotary_dim entries, divides
+    each value head by its root mean square and rotates it over its whole width by the token's position, writes q
+    in the cache's dtype and k and v into their page streams (which may differ in width).  The attention kernel reads
+    every key and value from the pages, this step's included, keeps scores, softmax weights and sums in float32,
+    and rotates each head's summed output back by the query's position before it stores it.  The angles come from
+    the rotary parts' per-step tables (cosine and sine of every token's angles, float32)."""
+
+    graph_safe = True
+
+    def __init__(self, spec: RotaryValueAttentionSpec, weights, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.k = runtime.kernels
+        self.w_qkv = torch.cat([weights[n] for n in (spec.q_proj, spec.k_proj, spec.v_proj)], dim=0).contiguous()
+        self.w_o = weights[spec.o_proj]
+        self.position = build_part(spec.position, weights, runtime) if spec.position is not None else None
+        self.value_position = build_part(spec.value_position, weights, runtime) if spec.value_position is not None else None
+        if self.value_position is not None and spec.value_position.rotary_dim != spec.value_head_dim:
+            raise ValueError("the values are rotated over their whole width")
+        self.width = spec.num_heads * spec.head_dim + spec.num_kv_heads * (spec.head_dim + spec.value_head_dim)
+
+    def forward(self, h, ctx, call):
+        s, k = self.spec, self.k
+        n = h.shape[0]
+        qkv = ctx.buffer("rva_qkv", (n, self.width), torch.float32)
+        k.linear(h, self.w_qkv, qkv)
+        kv = ctx.kv(call.cache)
+        pk, pv = kv.streams["k"], kv.streams["v"]
+        q = ctx.buffer("rva_q", (n, s.num_heads * s.head_dim), self.rt.act_dtype)
+        qk_table = self.position.table(ctx) if self.position is not None else None
+        v_table = self.value_position.table(ctx) if self.value_position is not None else None
+        k.rotary_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, s.value_head_dim, qk_table,
+                       s.position.rotary_dim if s.position is not None else 0,
+                       bool(s.position.interleaved) if s.position is not None else False,
+                       s.eps if s.value_norm else None, v_table,
+                       bool(s.value_position.interleaved) if s.value_position is not None else False,
+                       q, pk, pv, kv.slot_mapping if call.store else None)
+        out = ctx.buffer("rva_out", (n, s.num_heads * s.value_head_dim), self.rt.act_dtype)
+        k.paged_attention_streams(q, s.num_heads, s.num_kv_heads, s.head_dim, s.value_head_dim, pk, pv, kv.block_tables,
+                                  ctx.cu_q, ctx.seq_lens, out, s.scale, s.window or 0, v_table,
+                                  bool(s.value_position.interleaved) if s.value_position is not None else False,
+                                  max_q_len=ctx.max_q_len, max_seq_len=ctx.max_seq_len)
+        delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
+        k.linear(out, self.w_o, delta)
+        return delta
+
+
+register_part(RotaryValueAttentionSpec, RotaryValueAttention)

@@ -3,7 +3,8 @@
 The rule is the reference's (src/infurnace/executor/tinygrad/weights.py:42-55): the set
 of names in the files must equal the inventory, every shape must match, and all of this
 is checked before any tensor is read or converted
-(tests/test_model_weights.py:80-103).  One :class:`WeightError` lists everything that is
+(tests/test_model_weights.py:80-103).  A size that the inventory leaves open (None) is the file's to give; a
+tensor marked optional may be absent.  One :class:`WeightError` lists everything that is
 wrong: missing tensors, unexpected tensors and wrong shapes.  One exception to "equal":
 a tied model's folder may also store the head under its own name; the reference demands
 that head and embedding be one object (weights.py:68, model.py:34-36), so here the stored
@@ -31,7 +32,7 @@ def check_inventory(found: Mapping[str, tuple], expected: Mapping[str, "object"]
     """``found``: name -> (dtype tag, shape).  ``duplicates``: names that may be present beside the
     inventory, each with the tensor it must copy (same shape and dtype here; the bytes are compared by
     the caller).  Raises one error naming every fault."""
-    missing = sorted(set(expected) - set(found))
+    missing = sorted(n for n in set(expected) - set(found) if not getattr(expected[n], "optional", False))
     unexpected = sorted(set(found) - set(expected) - set(duplicates))
     wrong = []
     for name, of in sorted(duplicates.items()):
@@ -41,7 +42,7 @@ def check_inventory(found: Mapping[str, tuple], expected: Mapping[str, "object"]
     for name in sorted(set(expected) & set(found)):
         tag, shape = found[name]
         spec = expected[name]
-        if tuple(shape) != tuple(spec.shape):
+        if len(shape) != len(spec.shape) or any(b is not None and a != b for a, b in zip(shape, spec.shape)):
             wrong.append(f"{name}: expected {tuple(spec.shape)}, got {tuple(shape)}")
         elif spec.kind == "float" and tag not in _FLOAT_TAGS:
             wrong.append(f"{name}: expected a floating dtype, got {tag}")
@@ -93,6 +94,8 @@ def load_weights(model_dir: str, plan, engine_dtype, device, progress=None) -> D
         out = {}
         last = time.monotonic()
         for i, (name, spec) in enumerate(expected.items()):
+            if name not in found:            # an optional tensor that the folder does not hold
+                continue
             tag, _ = found[name]
             t = owner[name].tensor(name)
             out[name] = t.to(device=device, dtype=target_dtype(tag, spec.kind, engine_dtype), copy=True)

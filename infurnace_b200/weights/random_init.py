@@ -104,7 +104,7 @@ class DeviceRandomWeights(Mapping):
         norm weights in (default bfloat16); values are drawn in these and then follow the loader's dtype
         policy for ``engine_dtype``, so the tensors equal those of ``write_random_model`` + ``load_weights``."""
         import torch
-        self._specs = dict(plan.tensors())
+        self._specs = {n: t for n, t in plan.tensors().items() if not getattr(t, "optional", False)}
         self._seed, self._engine_dtype = seed, engine_dtype
         self._store = store_dtype or torch.bfloat16
         self._norm_store = norm_dtype or self._store
@@ -152,8 +152,12 @@ def write_random_model(config, seed: int, out_dir: str, store_dtype: str = "bflo
     norm_dt = getattr(torch, norm_dtype or store_dtype)
     items = []
     for name, spec in plan.tensors().items():
+        if getattr(spec, "optional", False):
+            continue
         if spec.kind == "int":
             raise NotImplementedError("random integer tables")
+        if any(s is None for s in spec.shape):
+            raise ValueError(f"tensor {name} has a size that only a stored file gives; name it in the configuration")
         items.append((name, _Producer(seed, name, spec.shape, norm_dt if len(spec.shape) <= 1 else mat_dt, kernels,
                                       init=spec.init)))
     write_safetensors(os.path.join(out_dir, "model.safetensors"), items,

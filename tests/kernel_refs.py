@@ -78,6 +78,8 @@ class ReferenceKernels:
             y = torch.sigmoid(y)
         elif epilogue == "gelu_tanh":
             y = 0.5 * y * (1 + torch.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+        elif epilogue == "tanh":
+            y = torch.tanh(y)
         elif epilogue != "none":
             raise ValueError(epilogue)
         out.copy_(y.to(out.dtype))
@@ -286,6 +288,231 @@ class ReferenceKernels:
                 if gate is not None:
                     o = o * torch.sigmoid(gate[t, gate_col: gate_col + H * d].to(self.cd))
                 out[t] = o.to(out.dtype)
+
+    # ------------------------------------------------------------------ sandwich-norm blocks, loops, token side input
+    def residual_norm_update(self, x, y, post_weight, eps, out=None, next_weight=None):
+        """x += y / sqrt(mean(y^2) + eps) * post_weight (float32, in place).  ``out``: the updated rows for the next
+        product, x / sqrt(mean(x^2) + eps) * next_weight, or x itself when next_weight is None, in out's dtype."""
+        v = y.to(self.cd)
+        x.add_((v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps) * post_weight.to(self.cd)).to(x.dtype))
+        if out is not None:
+            u = x.to(self.cd)
+            if next_weight is not None:
+                u = u / torch.sqrt(u.pow(2).mean(-1, keepdim=True) + eps) * next_weight.to(self.cd)
+            out.copy_(u.to(out.dtype))
+
+    def add_rows(self, x, rows=None, vec=None, accumulate=True):
+        """x (+)= rows + vec: rows float32 of x's shape, vec one row for all."""
+        t = torch.zeros_like(x, dtype=self.cd)
+        if accumulate:
+            t = t + x.to(self.cd)
+        if rows is not None:
+            t = t + rows.to(self.cd)
+        if vec is not None:
+            t = t + vec.to(self.cd)[None, :]
+        x.copy_(t.to(x.dtype))
+
+    def scaled_sum(self, total, d, scale, accumulate=True):
+        """total (+)= scale * d."""
+        t = d.to(self.cd) * scale
+        if accumulate:
+            t = t + total.to(self.cd)
+        total.copy_(t.to(total.dtype))
+
+    def token_side_gate(self, z, table, ids, offset, activation, out):
+        """out[n, j] = act(z[n, j]) * table[ids[n], offset + j]."""
+        y = z.to(self.cd)
+        if activation == "gelu_tanh":
+            y = 0.5 * y * (1 + torch.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+        elif activation == "silu":
+            y = y * torch.sigmoid(y)
+        else:
+            raise ValueError(activation)
+        out.copy_((y * table[ids.long(), offset: offset + z.shape[1]].to(self.cd)).to(out.dtype))
+
+    def softcap(self, logits, cap):
+        logits.copy_((cap * torch.tanh(logits.to(self.cd) / cap)).to(logits.dtype))
+
+    # ------------------------------------------------------------------ recurrences with state slots
+    def token_shift_mix(self, h, last, state_slots, cu_q, seq_lens, mu, out):
+        """out[s, t] = h[t] + (h'[t] - h[t]) * mu[s], h' the row before t in its request, or for a request's first
+        row of the step last[slot] (which then becomes the request's last row of the step)."""
+        for r in range(seq_lens.numel()):
+            if int(seq_lens[r]) <= 0:
+                continue
+            a, b, slot = int(cu_q[r]), int(cu_q[r + 1]), int(state_slots[r])
+            cur = h[a:b].to(self.cd)
+            prev = torch.cat((last[slot].to(self.cd)[None, :], cur[:-1]), dim=0)
+            for s_ in range(mu.shape[0]):
+                out[s_, a:b] = (cur + (prev - cur) * mu[s_].to(self.cd)).to(out.dtype)
+            last[slot] = cur[-1].to(last.dtype)
+
+    def linear_scan(self, q, k, v, w, heads, dim, vdim, state, state_slots, cu_q, seq_lens, out, eps, decay=None, w_bias=None,
+                    key_scale=1.0, bonus=None, norm_weight=None, gate=None, max_q_len=1):
+        """Per request and head, token by token on state[slot] [heads, dim, vdim] (float32): with the decay
+        d = decay[head] (constant) or exp(-exp(w + w_bias)) per key channel, kk = k * key_scale:
+        without bonus  S = d S + kk v^T, o = S^T q;  with bonus u  o = (S + u kk v^T)^T q, then S = d S + kk v^T.
+        out = o / rms(o) per head (* norm_weight [heads * vdim]) (* silu(gate))."""
+        for r in range(seq_lens.numel()):
+            if int(seq_lens[r]) <= 0:
+                continue
+            slot = int(state_slots[r])
+            S = state[slot].to(self.cd)
+            for t in range(int(cu_q[r]), int(cu_q[r + 1])):
+                qt = q[t].to(self.cd).view(heads, dim)
+                kt = k[t].to(self.cd).view(heads, dim) * key_scale
+                vt = v[t].to(self.cd).view(heads, vdim)
+                if decay is not None:
+                    d = decay.to(self.cd)[:, None].expand(heads, dim)
+                else:
+                    d = torch.exp(-torch.exp(w[t].to(self.cd) + w_bias.to(self.cd))).view(heads, dim)
+                kv = kt[:, :, None] * vt[:, None, :]
+                if bonus is not None:
+                    o = torch.einsum("hde,hd->he", S + bonus.to(self.cd).view(heads, dim)[:, :, None] * kv, qt)
+                    S = d[:, :, None] * S + kv
+                else:
+                    S = d[:, :, None] * S + kv
+                    o = torch.einsum("hde,hd->he", S, qt)
+                o = (o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps)).reshape(heads * vdim)
+                if norm_weight is not None:
+                    o = o * norm_weight.to(self.cd)
+                if gate is not None:
+                    g = gate[t].to(self.cd)
+                    o = o * g * torch.sigmoid(g)
+                out[t] = o.to(out.dtype)
+            state[slot] = S.to(state.dtype)
+
+    def gated_unit_scan(self, proj, z_bias, x_bias, state, state_slots, cu_q, seq_lens, out):
+        """proj [n, 3 width] holds z_raw | x_raw | g.  z = sigmoid(z_raw + z_bias), u = x_raw + x_bias,
+        c = u + 1/2 where u >= 0 else sigmoid(u); S = (1 - z) S + z c on state[slot] [width]; out = S * silu(g)."""
+        n = state.shape[1]
+        for r in range(seq_lens.numel()):
+            if int(seq_lens[r]) <= 0:
+                continue
+            slot = int(state_slots[r])
+            S = state[slot].to(self.cd)
+            for t in range(int(cu_q[r]), int(cu_q[r + 1])):
+                row = proj[t].to(self.cd)
+                z = torch.sigmoid(row[:n] + z_bias.to(self.cd))
+                u = row[n:2 * n] + x_bias.to(self.cd)
+                c = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+                S = (1 - z) * S + z * c
+                g = row[2 * n:]
+                out[t] = (S * g * torch.sigmoid(g)).to(out.dtype)
+            state[slot] = S.to(state.dtype)
+
+    # ------------------------------------------------------------------ attention with rotated values
+    @staticmethod
+    def _turn(t, cos, sin, dims, interleaved):
+        """Rotate the first ``dims`` entries of the last axis of t [n, heads, d]; cos, sin [n, 1, dims / 2]."""
+        out = t.clone()
+        if interleaved:
+            a, b = t[..., 0:dims:2], t[..., 1:dims:2]
+            out[..., 0:dims:2], out[..., 1:dims:2] = a * cos - b * sin, b * cos + a * sin
+        else:
+            a, b = t[..., : dims // 2], t[..., dims // 2: dims]
+            out[..., : dims // 2], out[..., dims // 2: dims] = a * cos - b * sin, b * cos + a * sin
+        return out
+
+    def _table(self, table):
+        pairs = table.view(table.shape[0], -1, 2).to(self.cd)
+        return pairs[..., 0][:, None, :], pairs[..., 1][:, None, :]
+
+    def rotary_store(self, qkv, num_heads, num_kv_heads, head_dim, value_head_dim, qk_table, rotary_dim, interleaved, value_eps,
+                     v_table, v_interleaved, q_out, k_pages, v_pages, slot_mapping):
+        """qkv [n, H d + G d + G dv].  q and k are rotated by the angles of qk_table ([n, rotary_dim] (cos, sin)
+        pairs; None: not rotated); each value head is divided by its root mean square (value_eps None: not) and
+        rotated over its whole width by v_table (None: not).  q_out gets q; k and v go to their pages
+        [pages, G, page_size, width] at slot_mapping (None: nothing is stored)."""
+        n, H, G, d, dv = qkv.shape[0], num_heads, num_kv_heads, head_dim, value_head_dim
+        q = qkv[:, : H * d].to(self.cd).reshape(n, H, d)
+        k = qkv[:, H * d: (H + G) * d].to(self.cd).reshape(n, G, d)
+        v = qkv[:, (H + G) * d:].to(self.cd).reshape(n, G, dv)
+        if qk_table is not None:
+            c, s_ = self._table(qk_table)
+            q, k = self._turn(q, c, s_, rotary_dim, interleaved), self._turn(k, c, s_, rotary_dim, interleaved)
+        if value_eps is not None:
+            v = v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + value_eps)
+        if v_table is not None:
+            c, s_ = self._table(v_table)
+            v = self._turn(v, c, s_, dv, v_interleaved)
+        q_out.copy_(q.reshape(n, H * d).to(q_out.dtype))
+        if slot_mapping is not None:
+            ps = k_pages.shape[2]
+            for t in range(n):
+                s_ = int(slot_mapping[t])
+                if s_ >= 0:
+                    k_pages[s_ // ps, :, s_ % ps, :] = k[t].to(k_pages.dtype)
+                    v_pages[s_ // ps, :, s_ % ps, :] = v[t].to(v_pages.dtype)
+
+    def paged_attention_streams(self, q, num_heads, num_kv_heads, head_dim, value_head_dim, k_pages, v_pages, block_tables, cu_q,
+                                seq_lens, out, scale, window, out_table, out_interleaved, max_q_len=0, max_seq_len=0):
+        """Causal softmax attention of q [n, H d] over the keys and values of the request's pages (streams
+        [pages, G, page_size, width]); the output of every head is then rotated BACK by the angles of out_table (the
+        query token's row; None: not)."""
+        H, G, d, dv = num_heads, num_kv_heads, head_dim, value_head_dim
+        ps = k_pages.shape[2]
+        for r in range(seq_lens.numel()):
+            q0, q1, L = int(cu_q[r]), int(cu_q[r + 1]), int(seq_lens[r])
+            if L <= 0:
+                out[q0:q1] = 0
+                continue
+            for t in range(q0, q1):
+                p = L - (q1 - q0) + (t - q0)
+                first = max(0, p - window + 1) if window else 0
+                pos = torch.arange(first, p + 1)
+                pages = block_tables[r].long()[pos // ps]
+                kk = k_pages[pages, :, pos % ps, :].to(self.cd).repeat_interleave(H // G, dim=1)
+                vv = v_pages[pages, :, pos % ps, :].to(self.cd).repeat_interleave(H // G, dim=1)
+                a = torch.einsum("hd,shd->hs", q[t].to(self.cd).view(H, d), kk) * scale
+                o = torch.einsum("hs,shd->hd", torch.softmax(a, dim=-1), vv)[None]
+                if out_table is not None:
+                    c, s_ = self._table(out_table[t:t + 1])
+                    o = self._turn(o, c, -s_, dv, out_interleaved)
+                out[t] = o.reshape(H * dv).to(out.dtype)
+
+    # ------------------------------------------------------------------ routed experts
+    def moe_route(self, logits, top, ids, gates):
+        """ids[n] = the ``top`` largest logits' indices, largest first (the lower index among equals);
+        gates[n] = softmax over those logits."""
+        val, idx = torch.sort(logits.to(self.cd), dim=-1, descending=True, stable=True)
+        ids.copy_(idx[:, :top].to(ids.dtype))
+        gates.copy_(torch.softmax(val[:, :top], dim=-1).to(gates.dtype))
+
+    def moe_plan(self, ids, num_experts, offsets, perm, pos):
+        """The pairs (token, choice), numbered token * top + choice, listed by expert in ascending pair number:
+        offsets[e] .. offsets[e + 1] are expert e's places in ``perm``; pos[pair] is the pair's place."""
+        flat = ids.reshape(-1).long()
+        order = torch.sort(flat, stable=True).indices
+        perm.copy_(order.to(perm.dtype))
+        pos[order] = torch.arange(flat.numel(), dtype=pos.dtype)
+        counts = torch.bincount(flat, minlength=num_experts)
+        offsets[0] = 0
+        offsets[1:] = torch.cumsum(counts, 0).to(offsets.dtype)
+
+    def moe_linear(self, x, w, offsets, perm, top, out, epilogue="none"):
+        """Row i of ``out`` belongs to the expert e with offsets[e] <= i < offsets[e + 1] and is
+        x[perm[i] // top] @ w[e]^T (perm None: x[i]); epilogue "silu_gate" as in ``linear``."""
+        for e in range(w.shape[0]):
+            a, b = int(offsets[e]), int(offsets[e + 1])
+            if a == b:
+                continue
+            rows = x[(perm[a:b].long() // top)] if perm is not None else x[a:b]
+            y = rows.to(self.cd) @ w[e].to(self.cd).t()
+            if epilogue == "silu_gate":
+                half = y.shape[1] // 2
+                y = y[:, :half] * torch.sigmoid(y[:, :half]) * y[:, half:]
+            elif epilogue != "none":
+                raise ValueError(epilogue)
+            out[a:b] = y.to(out.dtype)
+
+    def moe_combine(self, y, pos, gates, out):
+        """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending."""
+        n, top = gates.shape
+        acc = torch.zeros(n, y.shape[1], dtype=self.cd)
+        for j in range(top):
+            acc = acc + gates[:, j].to(self.cd)[:, None] * y[pos.view(n, top)[:, j].long()].to(self.cd)
+        out.copy_(acc.to(out.dtype))
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):

@@ -176,19 +176,21 @@ __device__ __forceinline__ void store_from_f32(void* p, int dtype, size_t i, flo
 }
 
 // A function of one number applied to each element of a product before it is stored (the `epilogue` argument of the
-// products carries it in the bits above the lowest four): 0 none, 1 relu(y)^2, 2 silu, 3 sigmoid, 4 gelu (tanh form).
+// products carries it in the bits above the lowest four): 0 none, 1 relu(y)^2, 2 silu, 3 sigmoid, 4 gelu (tanh form), 5 tanh.
 #define IFB_UNARY_NONE 0
 #define IFB_UNARY_RELU2 1
 #define IFB_UNARY_SILU 2
 #define IFB_UNARY_SIGMOID 3
 #define IFB_UNARY_GELU_TANH 4
-#define IFB_UNARY_LAST 4
+#define IFB_UNARY_TANH 5
+#define IFB_UNARY_LAST 5
 __device__ __forceinline__ float ifb_unary(float y, int kind) {
   switch (kind) {
     case IFB_UNARY_RELU2: { const float r = fmaxf(y, 0.f); return r * r; }
     case IFB_UNARY_SILU: return y / (1.f + expf(-y));
     case IFB_UNARY_SIGMOID: return 1.f / (1.f + expf(-y));
     case IFB_UNARY_GELU_TANH: return 0.5f * y * (1.f + tanhf(0.7978845608028654f * (y + 0.044715f * y * y * y)));
+    case IFB_UNARY_TANH: return tanhf(y);
     default: return y;
   }
 }

@@ -1,0 +1,245 @@
+// A mixture of experts on the device, with no step that the host has to wait for: the router's choice, the list of
+// (token, choice) pairs by expert, the experts' products as grouped launches over that list, and the weighted sum.
+// Router arithmetic, the softmax over the chosen logits and the final sum are float32; the grouped product
+// multiplies in float32 whatever the storage (each output element is one thread's sum over k in ascending order, so
+// a row's result does not depend on which other rows share its tile).  These kernels take every size.
+#include "common.cuh"
+#include <math.h>
+
+// ------------------------------------------------------------------------------------------
+// ids[n][j], j < top: the indices of row n's `top` largest logits, largest first, the lower index among equals;
+// gates[n][j]: the softmax over those logits only.  A warp per row; a lane holds the logits e = lane, lane + 32, ...
+// (up to MR_PER_LANE * 32 experts); lane j keeps the j-th chosen logit (up to 32 choices).
+// ------------------------------------------------------------------------------------------
+constexpr int MR_PER_LANE = 8;
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ gates, int rows, int experts,
+                 int top) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float val[MR_PER_LANE];
+#pragma unroll
+  for (int j = 0; j < MR_PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    val[j] = e < experts ? logits[(size_t)row * experts + e] : -INFINITY;
+    if (val[j] != val[j]) val[j] = -INFINITY;          // a NaN is never chosen before a number
+  }
+  unsigned taken = 0;                                   // bit j: this lane's j-th logit is chosen already
+  float first = 0.f, mine = -INFINITY, sum = 0.f;       // lane j < top keeps the j-th chosen logit
+  for (int t = 0; t < top; ++t) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < MR_PER_LANE; ++j) {
+      const int e = lane + 32 * j;
+      if (e < experts && !((taken >> j) & 1u) && (val[j] > best || (val[j] == best && e < best_e))) { best = val[j]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if ((best_e & 31) == lane && best_e < experts) taken |= 1u << (best_e >> 5);
+    if (t == 0) first = best;
+    if (lane == t) mine = best;
+    if (lane == 0) ids[(size_t)row * top + t] = best_e < experts ? best_e : 0;
+  }
+  const float p = lane < top ? expf(mine - first) : 0.f;
+  sum = warp_sum(p);
+  if (lane < top) gates[(size_t)row * top + lane] = p / sum;
+}
+
+IFB_EXPORT int ifb_moe_route(const float* logits, int* ids, float* gates, int rows, int experts, int top, cudaStream_t stream) {
+  if (rows <= 0) return IFB_OK;
+  if (experts < 1 || experts > 32 * MR_PER_LANE || top < 1 || top > experts || top > 32) return IFB_ERR_SIZE;
+  return ifb_launch(moe_route_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, logits, ids, gates, rows, experts, top);
+}
+
+// ------------------------------------------------------------------------------------------
+// The pairs (row, choice), numbered row * top + choice, listed by expert in ascending pair number: expert e's places
+// in `perm` are offsets[e] .. offsets[e + 1]; pos[pair] is the pair's place.  A block per expert: it counts the pairs
+// of lower experts (its offset), then walks the pairs in order, a block-wide prefix sum placing its own.
+// ------------------------------------------------------------------------------------------
+constexpr int MP_THREADS = 256;
+__global__ void __launch_bounds__(MP_THREADS)
+moe_plan_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ offsets, int* __restrict__ perm,
+                int* __restrict__ pos) {
+  __shared__ int warp_tot[MP_THREADS / 32];
+  __shared__ int lower_s;
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int lower = 0;
+  for (int i = threadIdx.x; i < pairs; i += MP_THREADS) { const int id = ids[i]; lower += (id >= 0 && id < e) ? 1 : 0; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) lower += __shfl_xor_sync(0xffffffffu, lower, o);
+  if (lane == 0) warp_tot[warp] = lower;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int s = 0;
+    for (int w = 0; w < MP_THREADS / 32; ++w) s += warp_tot[w];
+    lower_s = s;
+  }
+  __syncthreads();
+  int base = lower_s;
+  if (threadIdx.x == 0) offsets[e] = base;
+  for (int i0 = 0; i0 < pairs; i0 += MP_THREADS) {
+    const int i = i0 + threadIdx.x;
+    const bool hit = i < pairs && ids[i] == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+    __syncthreads();                                 // the totals of the round before have been read
+    if (lane == 0) warp_tot[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < MP_THREADS / 32; ++w) { const int c = warp_tot[w]; if (w < warp) before += c; total += c; }
+    if (hit) {
+      const int place = base + before + __popc(ballot & ((1u << lane) - 1u));
+      perm[place] = i;
+      pos[i] = place;
+    }
+    base += total;
+  }
+  if (e == experts - 1 && threadIdx.x == 0) offsets[experts] = base;
+}
+
+IFB_EXPORT int ifb_moe_plan(const int* ids, int pairs, int experts, int* offsets, int* perm, int* pos, cudaStream_t stream) {
+  if (experts < 1) return IFB_ERR_SIZE;
+  if (pairs < 0) return IFB_ERR_ARG;
+  return ifb_launch(moe_plan_kernel, dim3(experts), dim3(MP_THREADS), 0, stream, ids, pairs, experts, offsets, perm, pos);
+}
+
+// ------------------------------------------------------------------------------------------
+// The grouped product.  Row i of `out` belongs to the expert e with offsets[e] <= i < offsets[e + 1] and is
+//     x[src(i)] w[e]^T,   src(i) = perm[i] / top (perm null: i),   w [experts][o_w][k]
+// GATED: w[e] holds o gate rows and then o up rows, and out[i][j] = silu(gate_j) * up_j.  A block is a tile of ML_ROWS
+// rows of one expert by ML_COLS outputs; block row y is the y-th tile in the order of the experts (each expert's rows
+// are tiled on their own; block rows beyond the last tile return).  A thread owns 2 rows x 4 outputs.
+// ------------------------------------------------------------------------------------------
+constexpr int ML_ROWS = 32, ML_COLS = 64, ML_K = 32, ML_THREADS = 256;
+template <typename TA, typename TW, typename TO, bool GATED>
+__global__ void __launch_bounds__(ML_THREADS)
+moe_linear_kernel(const TA* __restrict__ x, const TW* __restrict__ w, const int* __restrict__ offsets,
+                  const int* __restrict__ perm, int top, TO* __restrict__ out, int experts, int o, int k) {
+  __shared__ float As[ML_ROWS][ML_K + 1];
+  __shared__ float Ws[(GATED ? 2 : 1) * ML_COLS][ML_K + 1];
+  __shared__ int src[ML_ROWS];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  int e = 0, row0 = 0, row1 = 0, tile = blockIdx.y;
+  bool found = false;
+  for (; e < experts; ++e) {
+    const int a = offsets[e], b = offsets[e + 1];
+    const int tiles = (b - a + ML_ROWS - 1) / ML_ROWS;
+    if (tile < tiles) { row0 = a + tile * ML_ROWS; row1 = min(b, row0 + ML_ROWS); found = true; break; }
+    tile -= tiles;
+  }
+  if (!found) return;
+  const int col0 = blockIdx.x * ML_COLS;
+  const int o_w = GATED ? 2 * o : o;
+  const TW* we = w + (size_t)e * o_w * k;
+  if (threadIdx.x < ML_ROWS) {
+    const int i = row0 + threadIdx.x;
+    src[threadIdx.x] = i < row1 ? (perm ? perm[i] / top : i) : -1;
+  }
+  __syncthreads();
+  const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;       // rows 2 ty, 2 ty + 1; outputs 4 tx .. 4 tx + 3
+  float acc[2][4] = {}, up[2][4] = {};
+  for (int k0 = 0; k0 < k; k0 += ML_K) {
+    for (int idx = threadIdx.x; idx < ML_ROWS * ML_K; idx += ML_THREADS) {
+      const int r = idx / ML_K, kk = idx % ML_K;
+      const int s = src[r];
+      As[r][kk] = (s >= 0 && k0 + kk < k) ? to_f32<TA>(x[(size_t)s * k + k0 + kk]) : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < (GATED ? 2 : 1) * ML_COLS * ML_K; idx += ML_THREADS) {
+      const int c = idx / ML_K, kk = idx % ML_K;
+      const int half = c / ML_COLS, cc = c % ML_COLS;
+      const int feat = col0 + cc;
+      Ws[c][kk] = (feat < o && k0 + kk < k) ? to_f32<TW>(we[((size_t)half * o + feat) * k + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < ML_K; ++kk) {
+      const float a0 = As[2 * ty][kk], a1 = As[2 * ty + 1][kk];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float wv = Ws[4 * tx + j][kk];
+        acc[0][j] = fmaf(a0, wv, acc[0][j]);
+        acc[1][j] = fmaf(a1, wv, acc[1][j]);
+        if (GATED) {
+          const float uv = Ws[ML_COLS + 4 * tx + j][kk];
+          up[0][j] = fmaf(a0, uv, up[0][j]);
+          up[1][j] = fmaf(a1, uv, up[1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + 2 * ty + i;
+    if (row >= row1) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int feat = col0 + 4 * tx + j;
+      if (feat >= o) continue;
+      float y = acc[i][j];
+      if (GATED) y = y / (1.f + expf(-y)) * up[i][j];
+      out[(size_t)row * o + feat] = from_f32<TO>(y);
+    }
+  }
+}
+
+template <typename TA, typename TW, typename TO>
+static int ml_launch(const void* x, const void* w, const int* offsets, const int* perm, int top, void* out, int rows, int experts,
+                     int o, int k, int gated, cudaStream_t s) {
+  dim3 grid((o + ML_COLS - 1) / ML_COLS, (rows + ML_ROWS - 1) / ML_ROWS + experts);
+  if (grid.y > 65535) return IFB_ERR_SIZE;
+  if (gated)
+    return ifb_launch(moe_linear_kernel<TA, TW, TO, true>, grid, dim3(ML_THREADS), 0, s, (const TA*)x, (const TW*)w, offsets, perm,
+                      top, (TO*)out, experts, o, k);
+  return ifb_launch(moe_linear_kernel<TA, TW, TO, false>, grid, dim3(ML_THREADS), 0, s, (const TA*)x, (const TW*)w, offsets, perm,
+                    top, (TO*)out, experts, o, k);
+}
+
+// x and w share one dtype (float32 or bfloat16); out is float32 or x's dtype.  rows: the number of rows of `out`
+// (the pairs); o: outputs per row (with gated, w holds 2 o rows per expert).
+IFB_EXPORT int ifb_moe_linear(const void* x, int x_dtype, const void* w, int w_dtype, const int* offsets, const int* perm, int top,
+                              void* out, int out_dtype, int rows, int experts, int o, int k, int gated, cudaStream_t stream) {
+  if (rows <= 0 || o <= 0) return IFB_OK;
+  if (experts < 1 || k < 1 || top < 1) return IFB_ERR_SIZE;
+  if (x_dtype == IFB_F32 && w_dtype == IFB_F32 && out_dtype == IFB_F32)
+    return ml_launch<float, float, float>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+  if (x_dtype == IFB_BF16 && w_dtype == IFB_BF16 && out_dtype == IFB_F32)
+    return ml_launch<__nv_bfloat16, __nv_bfloat16, float>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+  if (x_dtype == IFB_BF16 && w_dtype == IFB_BF16 && out_dtype == IFB_BF16)
+    return ml_launch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+  return IFB_ERR_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------------
+// out[n][f] = sum_j gates[n][j] * y[pos[n * top + j]][f], j ascending, float32.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos, const float* __restrict__ gates,
+                   float* __restrict__ out, int top, int width) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int n = blockIdx.x;
+  for (int f = threadIdx.x; f < width; f += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j)
+      acc = fmaf(gates[(size_t)n * top + j], y[(size_t)pos[(size_t)n * top + j] * width + f], acc);
+    out[(size_t)n * width + f] = acc;
+  }
+}
+
+IFB_EXPORT int ifb_moe_combine(const float* y, const int* pos, const float* gates, float* out, int rows, int top, int width,
+                               cudaStream_t stream) {
+  if (rows <= 0 || width <= 0) return IFB_OK;
+  if (top < 1) return IFB_ERR_SIZE;
+  return ifb_launch(moe_combine_kernel, dim3(rows), dim3(256), 0, stream, y, pos, gates, out, top, width);
+}

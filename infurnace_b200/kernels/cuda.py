@@ -19,7 +19,7 @@ from .build import load_library
 F32, BF16 = 0, 1
 # the `epilogue` argument of the products: 0 plain, 1 silu_gate (w holds gate rows, then up rows), 16 * u: plain with the
 # unary function u applied to every element (csrc/common.cuh: ifb_unary)
-EPILOGUES = {"none": 0, "silu_gate": 1, "relu2": 16, "silu": 32, "sigmoid": 48, "gelu_tanh": 64}
+EPILOGUES = {"none": 0, "silu_gate": 1, "relu2": 16, "silu": 32, "sigmoid": 48, "gelu_tanh": 64, "tanh": 80}
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 _ERRORS = {1: "a dtype (or combination of dtypes) has no kernel", 2: "a size is outside what the kernel takes",
            3: "an address or row length breaks the kernel's alignment rule", 4: "arguments contradict each other"}
@@ -111,6 +111,10 @@ class CudaKernels:
         self.scan_block_min = int(os.environ.get("INFURNACE_SCAN_BLOCK_MIN", "97"))     # tokens of the longest request from
         self.scan_blocked_calls = 0                                                    # which the recurrence runs in blocks
         self._scan_scratch = None
+        self._hyb = None               # the library of sandwich-norm blocks, state recurrences, stream attention, routed experts
+        self._ls_scratch = None
+        self.linear_scan_blocked_calls = 0
+        self.stream_attention_calls = 0
         self._mix = None               # the library of post-norm sublayers, the gated recurrence and talking attention
         self._tc = None                # the tcgen05 library, loaded when a product first has more than tc_min_rows rows
         # device int: non-zero after a kernel recorded a fault it contained (a bounded barrier wait that gave up, a
@@ -839,6 +843,313 @@ class CudaKernels:
             # per SM the longest tile is the kernel's time; shares of at most a quarter of the keys even that out
             return max(1, min(4, reach // 128)) if tiles < 2 * self.sm_count else 1
         return max(1, min(self.sm_count // max(1, tiles), reach // 128, 32))
+
+    # ------------------------------------------------------------------ sandwich-norm blocks, state recurrences, routed experts
+    def _hyb_lib(self):
+        if self._hyb is None:
+            m = self._hyb = load_library("hybrid", progress=self._progress)
+            m.ifb_residual_norm_update.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int,
+                                                   c_int, c_int, c_void_p]
+            m.ifb_add_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+            m.ifb_scaled_sum.argtypes = [c_void_p, c_void_p, c_float, c_int, c_longlong, c_void_p]
+            m.ifb_token_side_gate.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
+                                              c_int, c_int, c_void_p]
+            m.ifb_softcap.argtypes = [c_void_p, c_float, c_longlong, c_void_p]
+            m.ifb_token_shift_mix.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                              c_int, c_int, c_int, c_void_p]
+            m.ifb_linear_scan_slabs.argtypes = [c_int, c_int]
+            m.ifb_linear_scan_scratch_floats.restype = c_longlong
+            m.ifb_linear_scan_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
+            m.ifb_linear_scan.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_int, c_void_p]
+            m.ifb_gated_unit_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+            m.ifb_rotary_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                                           c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
+                                           c_int, c_int, c_void_p]
+            m.ifb_rotate_rows.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+            m.ifb_paged_attention_streams.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int,
+                                                      c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                      c_int, c_float, c_int, c_void_p, c_int, c_void_p]
+            m.ifb_moe_route.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+            m.ifb_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+            m.ifb_moe_linear.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                         c_int, c_int, c_int, c_int, c_void_p]
+            m.ifb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        return self._hyb
+
+    def residual_norm_update(self, x, y, post_weight, eps, out=None, next_weight=None):
+        """x += y / sqrt(mean(y^2) + eps) * post_weight, row by row in float32.  ``out``: the updated rows for the next
+        product in out's dtype: x / sqrt(mean(x^2) + eps) * next_weight, or x itself when next_weight is None."""
+        _dense(x, "x", torch.float32), _dense(y, "y", torch.float32), _dense(post_weight, "post_weight")
+        n, hidden = x.shape
+        if y.shape != x.shape or post_weight.numel() != hidden:
+            raise KernelError("residual_norm_update: sizes of x, y and post_weight do not match")
+        if next_weight is not None and (out is None or _dense(next_weight, "next_weight").numel() != hidden):
+            raise KernelError("residual_norm_update: next_weight needs out and has the row's length")
+        if out is not None and _dense(out, "out").shape != x.shape:
+            raise KernelError("residual_norm_update: out has the shape of x")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_residual_norm_update(
+            x.data_ptr(), y.data_ptr(), post_weight.data_ptr(), _code(post_weight), _ptr(next_weight),
+            _code(next_weight) if next_weight is not None else 0, float(eps), _ptr(out), _code(out) if out is not None else 0,
+            n, hidden, self._stream()), "residual_norm_update")
+
+    def add_rows(self, x, rows=None, vec=None, accumulate=True):
+        """x (+)= rows + vec: rows float32 of x's shape, vec one row for all; each may be None."""
+        _dense(x, "x", torch.float32)
+        n, hidden = x.shape
+        if rows is not None and _dense(rows, "rows", torch.float32).shape != x.shape:
+            raise KernelError("add_rows: rows has the shape of x")
+        if vec is not None and _dense(vec, "vec").numel() != hidden:
+            raise KernelError("add_rows: vec has the row's length")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_add_rows(x.data_ptr(), _ptr(rows), _ptr(vec), _code(vec) if vec is not None else 0,
+                                            1 if accumulate else 0, n, hidden, self._stream()), "add_rows")
+
+    def scaled_sum(self, total, d, scale, accumulate=True):
+        """total (+)= scale * d (float32, same shape)."""
+        _dense(total, "total", torch.float32), _dense(d, "d", torch.float32)
+        if total.shape != d.shape:
+            raise KernelError("scaled_sum: total and d differ in shape")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_scaled_sum(total.data_ptr(), d.data_ptr(), float(scale), 1 if accumulate else 0, d.numel(),
+                                              self._stream()), "scaled_sum")
+
+    def token_side_gate(self, z, table, ids, offset, activation, out):
+        """out[n, j] = act(z[n, j]) * table[ids[n], offset + j]."""
+        _dense(z, "z", torch.float32), _dense(table, "table"), _dense(ids, "ids", torch.int32), _dense(out, "out")
+        n, dim = z.shape
+        unary = EPILOGUES.get(activation, 0) >> 4
+        if not unary:
+            raise KernelError(f"token_side_gate: activation {activation!r} is no unary function of the kernels")
+        if out.shape != z.shape or ids.numel() != n or table.dim() != 2:
+            raise KernelError("token_side_gate: sizes of z, ids and out do not match")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_token_side_gate(z.data_ptr(), table.data_ptr(), _code(table), table.shape[1], table.shape[0],
+                                                   ids.data_ptr(), int(offset), unary, out.data_ptr(), _code(out), n, dim,
+                                                   self._stream()), "token_side_gate")
+
+    def softcap(self, logits, cap):
+        """logits <- cap * tanh(logits / cap), in place."""
+        _dense(logits, "logits", torch.float32)
+        self.launches += 1
+        _check(self._hyb_lib().ifb_softcap(logits.data_ptr(), float(cap), logits.numel(), self._stream()), "softcap")
+
+    def token_shift_mix(self, h, last, state_slots, cu_q, seq_lens, mu, out):
+        """out[s, t] = h[t] + (h'[t] - h[t]) * mu[s]; h' is the row before t in its request, or, for a request's first
+        row of the step, last[slot], which then takes the request's last row of the step (csrc/sandwich.cu)."""
+        _dense(h, "h"), _dense(last, "last", torch.float32), _dense(mu, "mu", torch.float32), _dense(out, "out", h.dtype)
+        _dense(state_slots, "state_slots", torch.int32), _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
+        n, hidden = h.shape
+        r = seq_lens.numel()
+        if mu.dim() != 2 or mu.shape[1] != hidden or out.shape != (mu.shape[0], n, hidden) or last.shape[1:] != (hidden,) \
+                or cu_q.numel() != r + 1 or state_slots.numel() < r:
+            raise KernelError("token_shift_mix: sizes of h, last, mu, out and the request arrays do not match")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_token_shift_mix(h.data_ptr(), _code(h), last.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(),
+                                                   seq_lens.data_ptr(), mu.data_ptr(), out.data_ptr(), n, r, hidden, mu.shape[0],
+                                                   self._stream()), "token_shift_mix")
+
+    @staticmethod
+    def _rows_f32(t, name, n, width):
+        """(address, leading dimension) of a float32 matrix [n, width] whose rows are contiguous (a slice of columns)."""
+        if t.dtype != torch.float32 or not t.is_cuda or t.dim() != 2 or t.shape != (n, width) or (width > 1 and t.stride(1) != 1):
+            raise KernelError(f"{name} must be float32 [{n}, {width}] on the device with contiguous rows")
+        return t.data_ptr(), t.stride(0)
+
+    def linear_scan(self, q, k, v, w, heads, dim, vdim, state, state_slots, cu_q, seq_lens, out, eps, decay=None, w_bias=None,
+                    key_scale=1.0, bonus=None, norm_weight=None, gate=None, max_q_len=1):
+        """The recurrence of a matrix state per head over this step's tokens of every request (csrc/linear_scan.cu).
+        q, k, w [n, heads * dim], v, gate [n, heads * vdim]: float32, may be column slices.  ``decay`` float32 [heads]:
+        a constant decay per head; else the decay is exp(-exp(w + w_bias)).  ``bonus`` [heads * dim]: the output is read
+        before the token's update, the token's own k v^T weighted by the bonus.  out = o / rms(o) per head
+        (* norm_weight [heads * vdim]) (* silu(gate)).  From ``scan_block_min`` tokens on the requests are cut into blocks
+        of 64 tokens that run side by side (three launches)."""
+        n = out.shape[0]
+        r = seq_lens.numel()
+        hd, hv = heads * dim, heads * vdim
+        _dense(state, "state", torch.float32), _dense(out, "out")
+        _dense(state_slots, "state_slots", torch.int32), _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
+        pq, pk, pv = self._rows_f32(q, "q", n, hd), self._rows_f32(k, "k", n, hd), self._rows_f32(v, "v", n, hv)
+        pw = self._rows_f32(w, "w", n, hd) if w is not None else (0, 0)
+        pg = self._rows_f32(gate, "gate", n, hv) if gate is not None else (0, 0)
+        if (decay is None) == (w is None) or (w is None) != (w_bias is None):
+            raise KernelError("linear_scan: give either decay, or w with w_bias")
+        if decay is not None and _dense(decay, "decay", torch.float32).numel() != heads:
+            raise KernelError("linear_scan: decay has one number per head")
+        pdt = None
+        for t, size, name in ((w_bias, hd, "w_bias"), (bonus, hd, "bonus"), (norm_weight, hv, "norm_weight")):
+            if t is None:
+                continue
+            _dense(t, name)
+            if t.numel() != size or (pdt is not None and t.dtype != pdt):
+                raise KernelError(f"linear_scan: {name} has the wrong length or a dtype of its own")
+            pdt = t.dtype
+        if state.shape[1:] != (heads, dim, vdim) or out.shape != (n, hv) or cu_q.numel() != r + 1 or state_slots.numel() < r:
+            raise KernelError("linear_scan: sizes of state, out and the request arrays do not match")
+        lib = self._hyb_lib()
+        raw = None
+        slabs = int(lib.ifb_linear_scan_slabs(dim, vdim))
+        need = n * hv if slabs > 1 else 0
+        scratch = 0
+        blocked = max_q_len >= self.scan_block_min and dim <= 128
+        if blocked:
+            scratch = int(lib.ifb_linear_scan_scratch_floats(n, r, heads, dim, vdim))
+            self.linear_scan_blocked_calls += 1
+        if need + scratch:
+            if self._ls_scratch is None or self._ls_scratch.numel() < need + scratch:
+                self._ls_scratch = torch.empty(need + scratch, dtype=torch.float32, device="cuda")
+                self.scratch_generation += 1
+            raw = self._ls_scratch[:need] if need else None
+        self.launches += (3 if blocked else 1) + (1 if slabs > 1 else 0)
+        _check(lib.ifb_linear_scan(
+            pq[0], pq[1], pk[0], pk[1], pv[0], pv[1], pw[0], pw[1], pg[0], pg[1], _ptr(decay), _ptr(w_bias), _ptr(bonus),
+            _ptr(norm_weight), _CODES[pdt] if pdt is not None else 0, float(key_scale), float(eps), state.data_ptr(),
+            state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), _code(out), _ptr(raw),
+            self._ls_scratch[need:].data_ptr() if blocked else 0, r, n, heads, dim, vdim, self._stream()), "linear_scan")
+
+    def gated_unit_scan(self, proj, z_bias, x_bias, state, state_slots, cu_q, seq_lens, out):
+        """minGRU over this step's tokens of every request: proj [n, 3 width] float32 holds z_raw | x_raw | g
+        (csrc/linear_scan.cu); state [slots, width] float32."""
+        _dense(proj, "proj", torch.float32), _dense(state, "state", torch.float32), _dense(out, "out")
+        _dense(z_bias, "z_bias"), _dense(x_bias, "x_bias", z_bias.dtype)
+        _dense(state_slots, "state_slots", torch.int32), _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
+        n, width = out.shape
+        r = seq_lens.numel()
+        if proj.shape != (n, 3 * width) or state.shape[1:] != (width,) or z_bias.numel() != width or x_bias.numel() != width \
+                or cu_q.numel() != r + 1 or state_slots.numel() < r:
+            raise KernelError("gated_unit_scan: sizes of proj, biases, state, out and the request arrays do not match")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_gated_unit_scan(proj.data_ptr(), z_bias.data_ptr(), x_bias.data_ptr(), _code(z_bias),
+                                                   state.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(),
+                                                   out.data_ptr(), _code(out), r, n, width, self._stream()), "gated_unit_scan")
+
+    @staticmethod
+    def _stream_pages(t, name, heads, width, dtype):
+        """(address, elements between pages, page size) of a page stream [pages, heads, page_size, width]."""
+        if t.dtype != dtype or not t.is_cuda or t.dim() != 4 or t.shape[1] != heads or t.shape[3] != width \
+                or t.stride(3) != 1 or t.stride(2) != width or t.stride(1) != t.shape[2] * width:
+            raise KernelError(f"{name} is not a page stream [pages, {heads}, page_size, {width}] of {dtype}")
+        return t.data_ptr(), t.stride(0), t.shape[2]
+
+    def rotary_store(self, qkv, num_heads, num_kv_heads, head_dim, value_head_dim, qk_table, rotary_dim, interleaved, value_eps,
+                     v_table, v_interleaved, q_out, k_pages, v_pages, slot_mapping):
+        """Rotation of q and k, norm and rotation of v, q row and page stores in one launch (csrc/attention_streams.cu).
+        qkv float32 [n, H d + G d + G dv]; tables float32 (cos, sin) pairs per token; value_eps None: no value norm."""
+        _dense(qkv, "qkv", torch.float32), _dense(q_out, "q_out")
+        n = qkv.shape[0]
+        H, G, d, dv = num_heads, num_kv_heads, head_dim, value_head_dim
+        if qkv.shape[1] != H * d + G * (d + dv) or q_out.shape != (n, H * d):
+            raise KernelError("rotary_store: widths of qkv and q_out do not match the heads")
+        if qk_table is not None and _dense(qk_table, "qk_table", torch.float32).shape != (n, rotary_dim):
+            raise KernelError("rotary_store: qk_table is [tokens, rotary_dim]")
+        if v_table is not None and _dense(v_table, "v_table", torch.float32).shape != (n, dv):
+            raise KernelError("rotary_store: v_table is [tokens, value_head_dim]")
+        pk, pv, ps = (0, 0, 1), (0, 0, 1), 1
+        if slot_mapping is not None:
+            _dense(slot_mapping, "slot_mapping", torch.int32)
+            pk, pv = self._stream_pages(k_pages, "k_pages", G, d, q_out.dtype), self._stream_pages(v_pages, "v_pages", G, dv, q_out.dtype)
+            ps = pk[2]
+            if pv[2] != ps or slot_mapping.numel() != n:
+                raise KernelError("rotary_store: the streams differ in page size, or slot_mapping in length")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_rotary_store(
+            qkv.data_ptr(), qkv.shape[1], H, G, d, dv, _ptr(qk_table), int(rotary_dim), int(bool(interleaved)),
+            0 if value_eps is None else 1, float(value_eps or 0.0), _ptr(v_table), int(bool(v_interleaved)), q_out.data_ptr(),
+            _code(q_out), pk[0], pk[1], pv[0], pv[1], _ptr(slot_mapping), ps, n, self._stream()), "rotary_store")
+
+    def rotate_rows(self, rows, table, heads, width, dims, interleaved, back=False):
+        """rows [n, heads * width] in place: every head's first ``dims`` entries turned by the token's angles of
+        ``table`` ([n, dims] (cos, sin) pairs), forward or back."""
+        _dense(rows, "rows"), _dense(table, "table", torch.float32)
+        n = rows.shape[0]
+        if rows.shape[1] != heads * width or table.shape != (n, dims):
+            raise KernelError("rotate_rows: sizes of rows and table do not match")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_rotate_rows(rows.data_ptr(), _code(rows), table.data_ptr(), n, heads, width, dims,
+                                               int(bool(interleaved)), 1 if back else 0, self._stream()), "rotate_rows")
+
+    def paged_attention_streams(self, q, num_heads, num_kv_heads, head_dim, value_head_dim, k_pages, v_pages, block_tables, cu_q,
+                                seq_lens, out, scale, window, out_table, out_interleaved, max_q_len=0, max_seq_len=0):
+        """Causal softmax attention of q [n, H d] over key and value page streams (csrc/attention_streams.cu), float32
+        scores, weights and sums; each head's output is rotated back by the query token's angles of ``out_table``
+        ([n, dv] (cos, sin) pairs; None: not)."""
+        _dense(q, "q"), _dense(out, "out", q.dtype), _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
+        if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
+            raise KernelError("paged_attention_streams: block_tables must be int32 with unit stride along pages")
+        n, r = q.shape[0], seq_lens.numel()
+        H, G, d, dv = num_heads, num_kv_heads, head_dim, value_head_dim
+        if q.shape != (n, H * d) or out.shape != (n, H * dv) or cu_q.numel() != r + 1 or block_tables.shape[0] < r:
+            raise KernelError("paged_attention_streams: sizes of q, out, cu_q, seq_lens and block_tables do not match")
+        pk, pv = self._stream_pages(k_pages, "k_pages", G, d, q.dtype), self._stream_pages(v_pages, "v_pages", G, dv, q.dtype)
+        if pk[2] != pv[2]:
+            raise KernelError("paged_attention_streams: the streams differ in page size")
+        if out_table is not None and _dense(out_table, "out_table", torch.float32).shape != (n, dv):
+            raise KernelError("paged_attention_streams: out_table is [tokens, value_head_dim]")
+        self.launches += 1
+        self.stream_attention_calls += 1
+        _check(self._hyb_lib().ifb_paged_attention_streams(
+            q.data_ptr(), _code(q), pk[0], pk[1], pv[0], pv[1], block_tables.data_ptr(), block_tables.stride(0), cu_q.data_ptr(),
+            seq_lens.data_ptr(), out.data_ptr(), n, r, H, G, d, dv, pk[2], float(scale), int(window), _ptr(out_table),
+            int(bool(out_interleaved)), self._stream()), "paged_attention_streams")
+
+    def moe_route(self, logits, top, ids, gates):
+        """ids[n] = the indices of row n's ``top`` largest logits, largest first (the lower index among equals);
+        gates[n] = the softmax over those logits (csrc/moe.cu)."""
+        _dense(logits, "logits", torch.float32), _dense(ids, "ids", torch.int32), _dense(gates, "gates", torch.float32)
+        n, experts = logits.shape
+        if ids.shape != (n, top) or gates.shape != (n, top):
+            raise KernelError("moe_route: ids and gates are [rows, top]")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_moe_route(logits.data_ptr(), ids.data_ptr(), gates.data_ptr(), n, experts, int(top),
+                                             self._stream()), "moe_route")
+
+    def moe_plan(self, ids, num_experts, offsets, perm, pos):
+        """The (row, choice) pairs listed by expert in ascending pair number: offsets [experts + 1], perm [pairs]
+        (place -> pair), pos [pairs] (pair -> place), all int32."""
+        _dense(ids, "ids", torch.int32), _dense(offsets, "offsets", torch.int32), _dense(perm, "perm", torch.int32)
+        _dense(pos, "pos", torch.int32)
+        pairs = ids.numel()
+        if offsets.numel() != num_experts + 1 or perm.numel() != pairs or pos.numel() != pairs:
+            raise KernelError("moe_plan: sizes of offsets, perm and pos do not match")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_moe_plan(ids.data_ptr(), pairs, int(num_experts), offsets.data_ptr(), perm.data_ptr(),
+                                            pos.data_ptr(), self._stream()), "moe_plan")
+
+    def moe_linear(self, x, w, offsets, perm, top, out, epilogue="none"):
+        """Row i of ``out`` belongs to the expert e with offsets[e] <= i < offsets[e + 1] and is x[perm[i] // top] @ w[e]^T
+        (perm None: x[i]); w [experts, o, k]; epilogue "silu_gate": w[e] holds gate rows, then up rows."""
+        _dense(x, "x"), _dense(w, "w", x.dtype), _dense(offsets, "offsets", torch.int32), _dense(out, "out")
+        gated = epilogue == "silu_gate"
+        if epilogue not in ("none", "silu_gate"):
+            raise KernelError(f"moe_linear: epilogue {epilogue!r}; known: none, silu_gate")
+        rows, o = out.shape
+        experts, ow, k = w.shape
+        if x.shape[1] != k or ow != (2 * o if gated else o) or offsets.numel() != experts + 1:
+            raise KernelError("moe_linear: sizes of x, w, offsets and out do not match")
+        if perm is not None:
+            if _dense(perm, "perm", torch.int32).numel() != rows or rows != x.shape[0] * top:
+                raise KernelError("moe_linear: perm has a place for every (row, choice) pair")
+        elif x.shape[0] != rows:
+            raise KernelError("moe_linear: without perm, x has a row for each row of out")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_moe_linear(x.data_ptr(), _code(x), w.data_ptr(), _code(w), offsets.data_ptr(), _ptr(perm),
+                                              int(top), out.data_ptr(), _code(out), rows, experts, o, k, 1 if gated else 0,
+                                              self._stream()), "moe_linear")
+
+    def moe_combine(self, y, pos, gates, out):
+        """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending, float32."""
+        _dense(y, "y", torch.float32), _dense(pos, "pos", torch.int32), _dense(gates, "gates", torch.float32)
+        _dense(out, "out", torch.float32)
+        n, top = gates.shape
+        if pos.numel() != n * top or y.shape != (n * top, out.shape[1]) or out.shape[0] != n:
+            raise KernelError("moe_combine: sizes of y, pos, gates and out do not match")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_moe_combine(y.data_ptr(), pos.data_ptr(), gates.data_ptr(), out.data_ptr(), n, top,
+                                               out.shape[1], self._stream()), "moe_combine")
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, uniform, out):

@@ -198,3 +198,13 @@ def forward(cfg, weights, tokens, layer_outputs=None):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return logits
+
+
+def greedy(cfg, weights, prompt, max_tokens):
+    """The tokens greedy decoding appends to ``prompt`` (the whole sequence is recomputed for every token)."""
+    toks, out = list(prompt), []
+    for _ in range(max_tokens):
+        nxt = int(torch.argmax(forward(cfg, weights, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out

@@ -605,12 +605,54 @@ def design_configs(size):
     return kaf, qwen
 
 
+def hybrid_config(size):
+    """A Lunelorn config.json mapping at the width, depth, head sizes and ACTIVE parameter count of design_configs(size):
+    layers parallel (attention + minGRU), retention, wkv, parallel, ...; retention heads of the Kafunex recurrence's
+    shape; 8 experts of which 2 run, each a third of the dense feed-forward's width (gate, up and down against up and
+    down); a token side input of 32; no loop (the depth stays that of the other designs)."""
+    W, layers, H, G, d, rh, rd, rv, ff, _ = {
+        "s": (1024, 8, 16, 4, 64, 8, 64, 128, 3072, 512),
+        "m": (2048, 8, 16, 4, 128, 16, 64, 128, 6144, 1024),
+        "l": (4096, 8, 32, 8, 128, 32, 64, 128, 12288, 1024),
+    }[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff // 3}, "router": {"experts": 8, "top": 2}}
+    entries = []
+    for i in range(layers):
+        if i % 4 in (0, 3):
+            entries.append({"type": "parallel", "mlp": mlp, "mixer": {
+                "left": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "rot": {"base": 1e6, "dims": d // 2}, "scale": d ** -0.5},
+                "right": {"width": W // 2}, "left_scale": 1.0, "right_scale": 1.0}})
+        elif i % 4 == 1:
+            entries.append({"type": "retention", "mlp": mlp, "mixer": {
+                "heads": rh, "dim": rd, "vdim": rv, "decay": [1.0 - 2.0 ** (-5 - 3 * j / max(1, rh - 1)) for j in range(rh)]}})
+        else:
+            entries.append({"type": "wkv", "mlp": mlp, "mixer": {"heads": W // 64, "dim": 64, "rank": 64}})
+    return {"architecture": "Lunelorn", "layers": entries, "norm": {"eps": 1e-6}, "vocab": 32768, "width": W,
+            "token_side": {"dim": 32}, "logit_softcap": 30.0}
+
+
+def attention_shape(conf):
+    """(key/value heads, head size, chunk or None) of a design's attention layers, from its config.json mapping."""
+    if "layers" not in conf:
+        return conf["num_key_value_heads"], conf["head_dim"], None
+    for layer in conf["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            return m["kv_heads"], m["dim"], (m.get("mask") or {}).get("size")
+        if layer["type"] == "parallel":
+            return m["left"]["kv_heads"], m["left"]["dim"], None
+    return 1, 1, None
+
+
 class DesignTimer(KernelClassTimer):
     """Events around every launch of either design's kernels, with what each launch has to do at the least: tensor-core
     flops, float32 flops on the ordinary pipes, and bytes of device memory.  ``pairs``: (query, visible key) pairs of
     one attention call of the step, set by the caller (the step's composition decides it)."""
     METHODS = KernelClassTimer.METHODS + ("embed_sinusoid", "residual_postnorm", "cast_rows", "wide_norm_store", "gated_scan",
-                                          "attention_talk")
+                                          "attention_talk", "residual_norm_update", "add_rows", "scaled_sum", "token_side_gate",
+                                          "softcap", "token_shift_mix", "linear_scan", "gated_unit_scan", "rotary_store",
+                                          "rotate_rows", "paged_attention_streams", "moe_route", "moe_plan", "moe_linear",
+                                          "moe_combine")
 
     def __init__(self, kernels, vocab, pairs, key_bytes):
         super().__init__(kernels, vocab)
@@ -630,6 +672,20 @@ class DesignTimer(KernelClassTimer):
             n = proj.shape[0]
             cls, ff = "recurrence", 6 * n * heads * dim * vdim
             by = proj.numel() * 4 + out.numel() * out.element_size() + 2 * a[11].numel() * heads * dim * vdim * 4
+        elif name == "paged_attention_streams":
+            cls, tf, by = "attention", 2 * a[1] * (a[3] + a[4]) * self.pairs, self.key_bytes
+        elif name == "linear_scan":
+            q, heads, dim, vdim, out = a[0], a[4], a[5], a[6], a[11]
+            n = q.shape[0]
+            cls, ff = "recurrence", 6 * n * heads * dim * vdim
+            by = n * heads * (3 * dim + 2 * vdim) * 4 + out.numel() * out.element_size() + 2 * a[10].numel() * heads * dim * vdim * 4
+        elif name == "gated_unit_scan":
+            proj, out = a[0], a[7]
+            cls, ff, by = "recurrence", 10 * out.numel(), proj.numel() * 4 + out.numel() * out.element_size()
+        elif name == "moe_linear":
+            x, w, out = a[0], a[1], a[5]
+            experts = min(w.shape[0], out.shape[0])           # experts whose matrices a step has to read at the least
+            cls, tf, by = "products", 2 * out.shape[0] * w.shape[1] * w.shape[2], experts * w.shape[1] * w.shape[2] * w.element_size()
         elif name in ("linear", "linear_residual_norm"):
             x, w = a[0], a[1]
             cls = "lm_head" if w.shape[0] == self.vocab else "products"
@@ -685,7 +741,8 @@ def run_designs(args):
     results = {}
     for size in args.design_sizes.split(","):
         kaf, qwen = design_configs(size)
-        for design, conf in (("kafunex", kaf), ("qwen3", qwen)):
+        pair = (("lunelorn", hybrid_config(size)), ("kafunex", kaf)) if args.hybrid else (("kafunex", kaf), ("qwen3", qwen))
+        for design, conf in pair:
             pool = batch * (context + 64) + PREFILL_TOKENS + 64
             opts = EngineOptions(dtype="bfloat16", page_size=16, num_pages=pool // 16, max_num_seqs=batch,
                                  max_num_batched_tokens=PREFILL_TOKENS, max_model_len=context + 64)
@@ -693,8 +750,7 @@ def run_designs(args):
             runner, plan = eng.runner, eng.plan
             vocab = plan.vocab_size
             params = sum(math.prod(t.shape) for t in plan.tensors().values())
-            chunks = [getattr(getattr(l, "mixer", None), "chunk", None) for l in plan.layers]
-            chunk = next((c for c in chunks if c), None)
+            G_, d_, chunk = attention_shape(conf)
             ms = time_prefill(runner, vocab, 3)
             pre = statistics.median(ms)
             rids = fill_contexts(runner, batch, context)
@@ -707,8 +763,6 @@ def run_designs(args):
             # where the time goes: an eager pass with events around every launch
             K = runner.rt.kernels
             graphs, runner.use_graphs = runner.use_graphs, False
-            G_, d_ = (conf["layers"][0]["mixer"]["kv_heads"], conf["layers"][0]["mixer"]["dim"]) if design == "kafunex" \
-                else (conf["num_key_value_heads"], conf["head_dim"])
             toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(2)).tolist()
             runner.cache.add_request("kp")
             with DesignTimer(K, vocab, visible_pairs(chunk, range(PREFILL_TOKENS)), 2 * PREFILL_TOKENS * G_ * d_ * 2) as t:
@@ -825,6 +879,8 @@ def main():
     ap.add_argument("--eager", action="store_true", help="launch every kernel of a decode step instead of replaying a graph")
     ap.add_argument("--designs", action="store_true",
                     help="instead of the default workload: the Kafunex design beside Qwen3 at equal sizes (prefill and decode)")
+    ap.add_argument("--hybrid", action="store_true",
+                    help="with --designs: the Lunelorn design beside Kafunex (equal width, depth and active parameters)")
     ap.add_argument("--design-sizes", default="s,m", help="with --designs: which of the sizes s, m, l (commas between)")
     ap.add_argument("--kernels-alone", action="store_true",
                     help="with --designs: only the talking attention and the gated recurrence, each alone (a small case)")

@@ -107,12 +107,15 @@ IFB_EXPORT int ifb_rotate_rows(void* rows, int dtype, const float* table, int n,
   if (n <= 0) return IFB_OK;
   if (heads < 1 || d < 1 || dims < 2 || dims % 2 || dims > d) return IFB_ERR_ARG;
   const size_t smem = (size_t)heads * d * sizeof(float);
-  if (smem > 48 * 1024) return IFB_ERR_SIZE;
+  if (smem > 200 * 1024) return IFB_ERR_SIZE;
   const float sign = back ? -1.f : 1.f;
-  if (dtype == IFB_BF16)
+  if (dtype == IFB_BF16) {
+    IFB_ALLOW_SMEM(rotate_rows_kernel<__nv_bfloat16>, smem);
     return ifb_launch(rotate_rows_kernel<__nv_bfloat16>, dim3(n), dim3(128), smem, stream, (__nv_bfloat16*)rows, table, heads, d, dims,
                       interleaved, sign);
+  }
   if (dtype != IFB_F32) return IFB_ERR_DTYPE;
+  IFB_ALLOW_SMEM(rotate_rows_kernel<float>, smem);
   return ifb_launch(rotate_rows_kernel<float>, dim3(n), dim3(128), smem, stream, (float*)rows, table, heads, d, dims, interleaved, sign);
 }
 

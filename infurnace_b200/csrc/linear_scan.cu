@@ -436,12 +436,119 @@ gated_unit_scan_kernel(const float* __restrict__ proj, const void* __restrict__ 
   *sp = S;
 }
 
+// Long portions of the gated unit, in chunks of GU_CHUNK tokens that run side by side, in two launches.  The recurrence
+// is S = a S + b with a = 1 - z and b = z cand, so a chunk is the map S -> A S + B with A the product of its a and B its
+// own end state from zero.  (A) every chunk forms (A, B); the request's first chunk also copies the slot's state aside.
+// (B) every chunk folds the maps of the request's earlier chunks onto that copy, in order, walks its tokens from there and
+// writes outputs; the request's last chunk writes the slot.  Differs from the one-launch walk by rounding only.
+constexpr int GU_CHUNK = 64;
+
+// The chunk that block row `row` is: request r, tokens t0 .. t1, its index j among the request's chunks, and the block row
+// of the request's first chunk.  False: the row is beyond the last chunk.
+__device__ __forceinline__ bool gu_find_chunk(const int* cu_q, const int* seq_lens, int requests, int row, int& r, int& t0, int& t1,
+                                              int& j, int& first_row, bool& last) {
+  int base = 0;
+  for (int i = 0; i < requests; ++i) {
+    const int ql = seq_lens[i] > 0 ? cu_q[i + 1] - cu_q[i] : 0;
+    const int chunks = (ql + GU_CHUNK - 1) / GU_CHUNK;
+    if (row - base < chunks) {
+      r = i; j = row - base; first_row = base;
+      t0 = cu_q[i] + j * GU_CHUNK;
+      t1 = min(cu_q[i + 1], t0 + GU_CHUNK);
+      last = j == chunks - 1;
+      return true;
+    }
+    base += chunks;
+  }
+  return false;
+}
+
+template <typename T, bool WRITE>
+__global__ void __launch_bounds__(128)
+gated_unit_chunk_kernel(const float* __restrict__ proj, const void* __restrict__ z_bias, const void* __restrict__ x_bias,
+                        int b_dtype, float* __restrict__ state, const int* __restrict__ state_slots,
+                        const int* __restrict__ cu_q, const int* __restrict__ seq_lens, T* __restrict__ out, int width,
+                        int requests, float* __restrict__ maps, float* __restrict__ init) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  int r, t0, t1, j, first_row;
+  bool last;
+  if (c >= width || !gu_find_chunk(cu_q, seq_lens, requests, blockIdx.y, r, t0, t1, j, first_row, last)) return;
+  const float bz = load_as_f32(z_bias, b_dtype, c), bx = load_as_f32(x_bias, b_dtype, c);
+  float* sp = state + (size_t)state_slots[r] * width + c;
+  float S = 0.f, A = 1.f;
+  if (WRITE) {
+    S = init[(size_t)r * width + c];
+    for (int i = 0; i < j; ++i) {
+      const float2 m = *reinterpret_cast<const float2*>(maps + 2 * ((size_t)(first_row + i) * width + c));
+      S = fmaf(m.x, S, m.y);
+    }
+  } else if (j == 0) {
+    init[(size_t)r * width + c] = *sp;
+  }
+  const size_t ld = 3 * (size_t)width;
+  for (int g0 = t0; g0 < t1; g0 += 8) {
+    float zr[8], xr[8], gr[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool in = g0 + i < t1;
+      const float* row = proj + (size_t)(g0 + i) * ld;
+      zr[i] = in ? row[c] : 0.f;
+      xr[i] = in ? row[width + c] : 0.f;
+      gr[i] = (in && WRITE) ? row[2 * width + c] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (g0 + i >= t1) break;
+      const float z = 1.f / (1.f + expf(-(zr[i] + bz)));
+      const float u = xr[i] + bx;
+      const float cand = u >= 0.f ? u + 0.5f : 1.f / (1.f + expf(-u));
+      S = fmaf(z, cand - S, S);
+      if (WRITE) out[(size_t)(g0 + i) * width + c] = from_f32<T>(S * (gr[i] / (1.f + expf(-gr[i]))));
+      else A *= 1.f - z;
+    }
+  }
+  if (!WRITE) *reinterpret_cast<float2*>(maps + 2 * ((size_t)blockIdx.y * width + c)) = make_float2(A, S);
+  else if (last) *sp = S;
+}
+
+// Floats of scratch that the chunked form needs.
+IFB_EXPORT long long ifb_gated_unit_scratch_floats(int tokens, int requests, int width) {
+  const long long rows = (tokens + GU_CHUNK - 1) / GU_CHUNK + requests;
+  return (2 * rows + requests) * (long long)width;
+}
+
+template <typename T>
+static int gu_chunked(const float* proj, const void* z_bias, const void* x_bias, int b_dtype, float* state, const int* state_slots,
+                      const int* cu_q, const int* seq_lens, void* out, int requests, int tokens, int width, float* scratch,
+                      cudaStream_t stream) {
+  const int rows = (tokens + GU_CHUNK - 1) / GU_CHUNK + requests;
+  if (rows > 65535) return IFB_ERR_SIZE;
+  float* maps = scratch;
+  float* init = scratch + 2 * (size_t)rows * width;
+  dim3 grid((width + 127) / 128, rows);
+  int st = ifb_launch(gated_unit_chunk_kernel<T, false>, grid, dim3(128), 0, stream, proj, z_bias, x_bias, b_dtype, state, state_slots,
+                      cu_q, seq_lens, (T*)out, width, requests, maps, init);
+  if (st != IFB_OK) return st;
+  return ifb_launch(gated_unit_chunk_kernel<T, true>, grid, dim3(128), 0, stream, proj, z_bias, x_bias, b_dtype, state, state_slots,
+                    cu_q, seq_lens, (T*)out, width, requests, maps, init);
+}
+
 IFB_EXPORT int ifb_gated_unit_scan(const float* proj, const void* z_bias, const void* x_bias, int b_dtype, float* state,
                                    const int* state_slots, const int* cu_q, const int* seq_lens, void* out, int out_dtype,
-                                   int requests, int tokens, int width, cudaStream_t stream) {
+                                   int requests, int tokens, int width, float* scratch, cudaStream_t stream) {
   if (requests <= 0 || tokens <= 0 || width <= 0) return IFB_OK;
   if (requests > 65535) return IFB_ERR_SIZE;
   if (b_dtype != IFB_F32 && b_dtype != IFB_BF16) return IFB_ERR_DTYPE;
+  if (scratch) {          // ifb_gated_unit_scratch_floats(...) floats: the chunked form
+    if (out_dtype == IFB_BF16)
+      return gu_chunked<__nv_bfloat16>(proj, z_bias, x_bias, b_dtype, state, state_slots, cu_q, seq_lens, out, requests, tokens,
+                                       width, scratch, stream);
+    if (out_dtype != IFB_F32) return IFB_ERR_DTYPE;
+    return gu_chunked<float>(proj, z_bias, x_bias, b_dtype, state, state_slots, cu_q, seq_lens, out, requests, tokens, width,
+                             scratch, stream);
+  }
   dim3 grid((width + 127) / 128, requests);
   if (out_dtype == IFB_BF16)
     return ifb_launch(gated_unit_scan_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, proj, z_bias, x_bias, b_dtype, state,

@@ -193,6 +193,137 @@ moe_linear_kernel(const TA* __restrict__ x, const TW* __restrict__ w, const int*
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// The grouped product on tensor cores (bfloat16 operands, float32 accumulation): mma.sync m16n8k16.  A CTA of four
+// warps is a tile of MM_ROWS rows of one expert by MM_COLS outputs (GATED: the gate and the up column of each output,
+// so that the activation is the epilogue); warp w owns rows 16 w .. 16 w + 15 of the tile.  The k range is walked in
+// steps of MM_K through two stages of shared memory filled by 16-byte asynchronous copies (rows gathered through the
+// pair list; rows and columns beyond the tile, and k beyond the end, are filled with zeros), fragments come out of
+// shared memory by ldmatrix from rows padded to 80 bytes (no bank conflicts).  A row's result depends on its own
+// operands only, whatever else shares its tile.  k must be a multiple of 8.
+// ------------------------------------------------------------------------------------------
+constexpr int MM_ROWS = 64, MM_COLS = 64, MM_K = 32, MM_PAD = 8, MM_THREADS = 128;
+
+__device__ __forceinline__ void mm_cp16(void* dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void mm_ldmatrix4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mm_mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(MM_THREADS)
+moe_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
+                      const int* __restrict__ perm, int top, TO* __restrict__ out, int experts, int o, int k) {
+  constexpr int WR = (GATED ? 2 : 1) * MM_COLS;              // weight rows of a tile
+  __shared__ __align__(16) __nv_bfloat16 As[2][MM_ROWS][MM_K + MM_PAD];
+  __shared__ __align__(16) __nv_bfloat16 Ws[2][WR][MM_K + MM_PAD];
+  __shared__ int src[MM_ROWS];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  int e = 0, row0 = 0, row1 = 0, tile = blockIdx.y;
+  bool found = false;
+  for (; e < experts; ++e) {
+    const int a = offsets[e], b = offsets[e + 1];
+    const int tiles = (b - a + MM_ROWS - 1) / MM_ROWS;
+    if (tile < tiles) { row0 = a + tile * MM_ROWS; row1 = min(b, row0 + MM_ROWS); found = true; break; }
+    tile -= tiles;
+  }
+  if (!found) return;
+  const int col0 = blockIdx.x * MM_COLS;
+  const int o_w = GATED ? 2 * o : o;
+  const __nv_bfloat16* we = w + (size_t)e * o_w * k;
+  if (threadIdx.x < MM_ROWS) {
+    const int i = row0 + threadIdx.x;
+    src[threadIdx.x] = i < row1 ? (perm ? perm[i] / top : i) : -1;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool warp_live = row0 + 16 * warp < row1;           // a warp whose 16 rows lie beyond the expert's rows only copies
+  auto fill = [&](int stage, int k0) {
+    for (int idx = threadIdx.x; idx < MM_ROWS * (MM_K / 8); idx += MM_THREADS) {
+      const int r = idx / (MM_K / 8), c = (idx % (MM_K / 8)) * 8;
+      const int s = src[r];
+      const bool ok = s >= 0 && k0 + c < k;
+      mm_cp16(&As[stage][r][c], ok ? x + (size_t)s * k + k0 + c : x, ok);
+    }
+    for (int idx = threadIdx.x; idx < WR * (MM_K / 8); idx += MM_THREADS) {
+      const int r = idx / (MM_K / 8), c = (idx % (MM_K / 8)) * 8;
+      const int half = r / MM_COLS, feat = col0 + r % MM_COLS;
+      const bool ok = feat < o && k0 + c < k;
+      mm_cp16(&Ws[stage][r][c], ok ? we + ((size_t)half * o + feat) * k + k0 + c : we, ok);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  float acc[MM_COLS / 8][4] = {}, up[GATED ? MM_COLS / 8 : 1][4] = {};
+  const int steps = (k + MM_K - 1) / MM_K;
+  fill(0, 0);
+  for (int st = 0; st < steps; ++st) {
+    if (st + 1 < steps) {
+      fill((st + 1) & 1, (st + 1) * MM_K);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+    const int cur = st & 1;
+    if (warp_live) {
+#pragma unroll
+      for (int kk = 0; kk < MM_K; kk += 16) {
+        unsigned a[4];
+        mm_ldmatrix4(a[0], a[1], a[2], a[3], &As[cur][16 * warp + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+        for (int nt = 0; nt < MM_COLS / 8; nt += 2) {
+          unsigned b0, b1, b2, b3;
+          const int brow = nt * 8 + (lane & 7) + (lane >> 4) * 8, bcol = kk + ((lane >> 3) & 1) * 8;
+          mm_ldmatrix4(b0, b1, b2, b3, &Ws[cur][brow][bcol]);
+          mm_mma(acc[nt], a, b0, b1);
+          mm_mma(acc[nt + 1], a, b2, b3);
+          if (GATED) {
+            mm_ldmatrix4(b0, b1, b2, b3, &Ws[cur][MM_COLS + brow][bcol]);
+            mm_mma(up[nt], a, b0, b1);
+            mm_mma(up[nt + 1], a, b2, b3);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (!warp_live) return;
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < MM_COLS / 8; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = row0 + 16 * warp + g + (i >> 1) * 8, feat = col0 + nt * 8 + 2 * t + (i & 1);
+      if (row >= row1 || feat >= o) continue;
+      float y = acc[nt][i];
+      if (GATED) y = y / (1.f + expf(-y)) * up[nt][i];
+      out[(size_t)row * o + feat] = from_f32<TO>(y);
+    }
+  }
+}
+
+template <typename TO>
+static int mm_launch(const void* x, const void* w, const int* offsets, const int* perm, int top, void* out, int rows, int experts,
+                     int o, int k, int gated, cudaStream_t s) {
+  dim3 grid((o + MM_COLS - 1) / MM_COLS, (rows + MM_ROWS - 1) / MM_ROWS + experts);
+  if (grid.y > 65535) return IFB_ERR_SIZE;
+  if (gated)
+    return ifb_launch(moe_linear_mma_kernel<TO, true>, grid, dim3(MM_THREADS), 0, s, (const __nv_bfloat16*)x,
+                      (const __nv_bfloat16*)w, offsets, perm, top, (TO*)out, experts, o, k);
+  return ifb_launch(moe_linear_mma_kernel<TO, false>, grid, dim3(MM_THREADS), 0, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                    offsets, perm, top, (TO*)out, experts, o, k);
+}
+
 template <typename TA, typename TW, typename TO>
 static int ml_launch(const void* x, const void* w, const int* offsets, const int* perm, int top, void* out, int rows, int experts,
                      int o, int k, int gated, cudaStream_t s) {
@@ -205,18 +336,29 @@ static int ml_launch(const void* x, const void* w, const int* offsets, const int
                     top, (TO*)out, experts, o, k);
 }
 
-// x and w share one dtype (float32 or bfloat16); out is float32 or x's dtype.  rows: the number of rows of `out`
-// (the pairs); o: outputs per row (with gated, w holds 2 o rows per expert).
+// x and w: float32 or bfloat16, in any mix; out: float32 or bfloat16.  rows: the number of rows of `out` (the pairs);
+// o: outputs per row (with gated, w holds 2 o rows per expert).  tensor_cores: bfloat16 x and w with k a multiple of 8
+// run the mma.sync kernel; everything else, and everything when it is 0, runs the plain kernel.
 IFB_EXPORT int ifb_moe_linear(const void* x, int x_dtype, const void* w, int w_dtype, const int* offsets, const int* perm, int top,
-                              void* out, int out_dtype, int rows, int experts, int o, int k, int gated, cudaStream_t stream) {
+                              void* out, int out_dtype, int rows, int experts, int o, int k, int gated, int tensor_cores,
+                              cudaStream_t stream) {
   if (rows <= 0 || o <= 0) return IFB_OK;
   if (experts < 1 || k < 1 || top < 1) return IFB_ERR_SIZE;
-  if (x_dtype == IFB_F32 && w_dtype == IFB_F32 && out_dtype == IFB_F32)
-    return ml_launch<float, float, float>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
-  if (x_dtype == IFB_BF16 && w_dtype == IFB_BF16 && out_dtype == IFB_F32)
-    return ml_launch<__nv_bfloat16, __nv_bfloat16, float>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
-  if (x_dtype == IFB_BF16 && w_dtype == IFB_BF16 && out_dtype == IFB_BF16)
-    return ml_launch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+  if (tensor_cores && x_dtype == IFB_BF16 && w_dtype == IFB_BF16 && k % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0)) {
+    if (out_dtype == IFB_F32) return mm_launch<float>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+    if (out_dtype == IFB_BF16) return mm_launch<__nv_bfloat16>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+    return IFB_ERR_DTYPE;
+  }
+#define ML_CASE(XD, WD, OD, TA, TW, TO)                                                                      \
+  if (x_dtype == XD && w_dtype == WD && out_dtype == OD)                                                     \
+    return ml_launch<TA, TW, TO>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+  ML_CASE(IFB_F32, IFB_F32, IFB_F32, float, float, float)
+  ML_CASE(IFB_BF16, IFB_BF16, IFB_F32, __nv_bfloat16, __nv_bfloat16, float)
+  ML_CASE(IFB_BF16, IFB_BF16, IFB_BF16, __nv_bfloat16, __nv_bfloat16, __nv_bfloat16)
+  ML_CASE(IFB_BF16, IFB_F32, IFB_F32, __nv_bfloat16, float, float)
+  ML_CASE(IFB_BF16, IFB_F32, IFB_BF16, __nv_bfloat16, float, __nv_bfloat16)
+  ML_CASE(IFB_F32, IFB_BF16, IFB_F32, float, __nv_bfloat16, float)
+#undef ML_CASE
   return IFB_ERR_DTYPE;
 }
 

@@ -370,8 +370,15 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         before = getattr(self.rt.kernels, "launches", 0)
         ctx.shared.clear()             # what parts computed once for the step is computed in the recording too
-        with torch.cuda.graph(graph):
-            recorded = self._forward(ctx, sample, greedy)
+        import gc
+        collecting = gc.isenabled()
+        gc.disable()                   # a collection inside the recording could free pinned memory or older graphs, which a
+        try:                           # stream that is being recorded does not allow
+            with torch.cuda.graph(graph):
+                recorded = self._forward(ctx, sample, greedy)
+        finally:
+            if collecting:
+                gc.enable()
         self.launches_per_graph_step = getattr(self.rt.kernels, "launches", 0) - before
         self._graphs[key] = (graph, stamp, recorded)
         return logits

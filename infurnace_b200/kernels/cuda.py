@@ -113,6 +113,9 @@ class CudaKernels:
         self._scan_scratch = None
         self._hyb = None               # the library of sandwich-norm blocks, state recurrences, stream attention, routed experts
         self._ls_scratch = None
+        self._gu_scratch = None
+        self.gated_unit_chunked_calls = 0
+        self.moe_tensor_cores = os.environ.get("INFURNACE_MOE_MMA", "1") != "0"
         self.linear_scan_blocked_calls = 0
         self.stream_attention_calls = 0
         self._mix = None               # the library of post-norm sublayers, the gated recurrence and talking attention
@@ -865,7 +868,9 @@ class CudaKernels:
                                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                           c_int, c_void_p]
             m.ifb_gated_unit_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                              c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+                                              c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+            m.ifb_gated_unit_scratch_floats.restype = c_longlong
+            m.ifb_gated_unit_scratch_floats.argtypes = [c_int, c_int, c_int]
             m.ifb_rotary_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float,
                                            c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
                                            c_int, c_int, c_void_p]
@@ -876,7 +881,7 @@ class CudaKernels:
             m.ifb_moe_route.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
             m.ifb_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
             m.ifb_moe_linear.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-                                         c_int, c_int, c_int, c_int, c_void_p]
+                                         c_int, c_int, c_int, c_int, c_int, c_void_p]
             m.ifb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         return self._hyb
 
@@ -1011,9 +1016,10 @@ class CudaKernels:
             state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), _code(out), _ptr(raw),
             self._ls_scratch[need:].data_ptr() if blocked else 0, r, n, heads, dim, vdim, self._stream()), "linear_scan")
 
-    def gated_unit_scan(self, proj, z_bias, x_bias, state, state_slots, cu_q, seq_lens, out):
+    def gated_unit_scan(self, proj, z_bias, x_bias, state, state_slots, cu_q, seq_lens, out, max_q_len=1):
         """minGRU over this step's tokens of every request: proj [n, 3 width] float32 holds z_raw | x_raw | g
-        (csrc/linear_scan.cu); state [slots, width] float32."""
+        (csrc/linear_scan.cu); state [slots, width] float32.  From ``scan_block_min`` tokens on the requests are cut into
+        chunks of 64 tokens that run side by side (two launches), which differs by rounding only."""
         _dense(proj, "proj", torch.float32), _dense(state, "state", torch.float32), _dense(out, "out")
         _dense(z_bias, "z_bias"), _dense(x_bias, "x_bias", z_bias.dtype)
         _dense(state_slots, "state_slots", torch.int32), _dense(cu_q, "cu_q", torch.int32), _dense(seq_lens, "seq_lens", torch.int32)
@@ -1022,10 +1028,19 @@ class CudaKernels:
         if proj.shape != (n, 3 * width) or state.shape[1:] != (width,) or z_bias.numel() != width or x_bias.numel() != width \
                 or cu_q.numel() != r + 1 or state_slots.numel() < r:
             raise KernelError("gated_unit_scan: sizes of proj, biases, state, out and the request arrays do not match")
-        self.launches += 1
+        scratch = 0
+        if max_q_len >= self.scan_block_min:
+            need = int(self._hyb_lib().ifb_gated_unit_scratch_floats(n, r, width))
+            if self._gu_scratch is None or self._gu_scratch.numel() < need:
+                self._gu_scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+                self.scratch_generation += 1
+            scratch = self._gu_scratch.data_ptr()
+            self.gated_unit_chunked_calls += 1
+        self.launches += 2 if scratch else 1
         _check(self._hyb_lib().ifb_gated_unit_scan(proj.data_ptr(), z_bias.data_ptr(), x_bias.data_ptr(), _code(z_bias),
                                                    state.data_ptr(), state_slots.data_ptr(), cu_q.data_ptr(), seq_lens.data_ptr(),
-                                                   out.data_ptr(), _code(out), r, n, width, self._stream()), "gated_unit_scan")
+                                                   out.data_ptr(), _code(out), r, n, width, scratch, self._stream()),
+               "gated_unit_scan")
 
     @staticmethod
     def _stream_pages(t, name, heads, width, dtype):
@@ -1121,8 +1136,9 @@ class CudaKernels:
 
     def moe_linear(self, x, w, offsets, perm, top, out, epilogue="none"):
         """Row i of ``out`` belongs to the expert e with offsets[e] <= i < offsets[e + 1] and is x[perm[i] // top] @ w[e]^T
-        (perm None: x[i]); w [experts, o, k]; epilogue "silu_gate": w[e] holds gate rows, then up rows."""
-        _dense(x, "x"), _dense(w, "w", x.dtype), _dense(offsets, "offsets", torch.int32), _dense(out, "out")
+        (perm None: x[i]); w [experts, o, k]; epilogue "silu_gate": w[e] holds gate rows, then up rows.  bfloat16 x and w
+        with k a multiple of 8 run on tensor cores (mma.sync), everything else in plain float32 arithmetic."""
+        _dense(x, "x"), _dense(w, "w"), _dense(offsets, "offsets", torch.int32), _dense(out, "out")
         gated = epilogue == "silu_gate"
         if epilogue not in ("none", "silu_gate"):
             raise KernelError(f"moe_linear: epilogue {epilogue!r}; known: none, silu_gate")
@@ -1138,7 +1154,7 @@ class CudaKernels:
         self.launches += 1
         _check(self._hyb_lib().ifb_moe_linear(x.data_ptr(), _code(x), w.data_ptr(), _code(w), offsets.data_ptr(), _ptr(perm),
                                               int(top), out.data_ptr(), _code(out), rows, experts, o, k, 1 if gated else 0,
-                                              self._stream()), "moe_linear")
+                                              1 if self.moe_tensor_cores else 0, self._stream()), "moe_linear")
 
     def moe_combine(self, y, pos, gates, out):
         """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending, float32."""

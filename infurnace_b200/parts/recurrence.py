@@ -153,7 +153,8 @@ class GatedUnit:
         proj = ctx.buffer("gu_proj", (n, 3 * s.width), torch.float32)
         k.linear(h, self.w_all, proj)
         out = ctx.buffer("gu_out", (n, s.width), self.rt.act_dtype)
-        k.gated_unit_scan(proj, self.z_bias, self.x_bias, ctx.state(call.cache), ctx.state_slots, ctx.cu_q, ctx.seq_lens, out)
+        k.gated_unit_scan(proj, self.z_bias, self.x_bias, ctx.state(call.cache), ctx.state_slots, ctx.cu_q, ctx.seq_lens, out,
+                          max_q_len=ctx.max_q_len)
         delta = ctx.buffer("delta_unit", (n, s.hidden_size), torch.float32)
         k.linear(out, self.w_o, delta)
         return delta

@@ -29,7 +29,20 @@ class RotaryValueAttention:
         self.value_position = build_part(spec.value_position, weights, runtime) if spec.value_position is not None else None
         if self.value_position is not None and spec.value_position.rotary_dim != spec.value_head_dim:
             raise ValueError("the values are rotated over their whole width")
+        import os
+        self.exact_weights = os.environ.get("INFURNACE_EXACT_ATTENTION", "0") not in ("", "0")
         self.width = spec.num_heads * spec.head_dim + spec.num_kv_heads * (spec.head_dim + spec.value_head_dim)
+
+    def _on_tensor_cores(self, kv):
+        """bfloat16 with keys and values of one width in one tensor: the framework's tensor-core attention kernels run
+        (scores and softmax in float32; the weights are rounded to bfloat16 as the left operand of the P V product, which
+        accumulates in float32).  Everything else, and every step when ``exact_weights`` is set, runs the plain kernel,
+        which keeps the weights in float32 through the sum."""
+        s = self.spec
+        group = s.num_heads // s.num_kv_heads
+        return (not self.exact_weights and self.rt.act_dtype == torch.bfloat16 and kv.pages is not None
+                and s.head_dim == s.value_head_dim and s.head_dim % 16 == 0 and s.head_dim <= 256 and group <= 16
+                and hasattr(self.k, "rotate_rows"))
 
     def forward(self, h, ctx, call):
         s, k = self.spec, self.k
@@ -48,10 +61,18 @@ class RotaryValueAttention:
                        bool(s.value_position.interleaved) if s.value_position is not None else False,
                        q, pk, pv, kv.slot_mapping if call.store else None)
         out = ctx.buffer("rva_out", (n, s.num_heads * s.value_head_dim), self.rt.act_dtype)
-        k.paged_attention_streams(q, s.num_heads, s.num_kv_heads, s.head_dim, s.value_head_dim, pk, pv, kv.block_tables,
-                                  ctx.cu_q, ctx.seq_lens, out, s.scale, s.window or 0, v_table,
-                                  bool(s.value_position.interleaved) if s.value_position is not None else False,
-                                  max_q_len=ctx.max_q_len, max_seq_len=ctx.max_seq_len)
+        if self._on_tensor_cores(kv):
+            # the framework's tensor-core attention over the entry's one tensor of keys and values, then the turn back
+            k.paged_attention(q, s.num_heads, s.num_kv_heads, s.head_dim, kv.pages, kv.block_tables, ctx.cu_q, ctx.seq_lens, out,
+                              s.scale, s.window or 0, ctx.max_q_len, ctx.max_seq_len, min_q_len=ctx.min_q_len)
+            if v_table is not None:
+                k.rotate_rows(out, v_table, s.num_heads, s.value_head_dim, s.value_head_dim, bool(s.value_position.interleaved),
+                              back=True)
+        else:
+            k.paged_attention_streams(q, s.num_heads, s.num_kv_heads, s.head_dim, s.value_head_dim, pk, pv, kv.block_tables,
+                                      ctx.cu_q, ctx.seq_lens, out, s.scale, s.window or 0, v_table,
+                                      bool(s.value_position.interleaved) if s.value_position is not None else False,
+                                      max_q_len=ctx.max_q_len, max_seq_len=ctx.max_seq_len)
         delta = ctx.buffer("delta_mixer", (n, s.hidden_size), torch.float32)
         k.linear(out, self.w_o, delta)
         return delta

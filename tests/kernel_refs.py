@@ -382,7 +382,7 @@ class ReferenceKernels:
                 out[t] = o.to(out.dtype)
             state[slot] = S.to(state.dtype)
 
-    def gated_unit_scan(self, proj, z_bias, x_bias, state, state_slots, cu_q, seq_lens, out):
+    def gated_unit_scan(self, proj, z_bias, x_bias, state, state_slots, cu_q, seq_lens, out, max_q_len=1):
         """proj [n, 3 width] holds z_raw | x_raw | g.  z = sigmoid(z_raw + z_bias), u = x_raw + x_bias,
         c = u + 1/2 where u >= 0 else sigmoid(u); S = (1 - z) S + z c on state[slot] [width]; out = S * silu(g)."""
         n = state.shape[1]
@@ -444,6 +444,12 @@ class ReferenceKernels:
                 if s_ >= 0:
                     k_pages[s_ // ps, :, s_ % ps, :] = k[t].to(k_pages.dtype)
                     v_pages[s_ // ps, :, s_ % ps, :] = v[t].to(v_pages.dtype)
+
+    def rotate_rows(self, rows, table, heads, width, dims, interleaved, back=False):
+        """rows [n, heads * width] in place: every head's first ``dims`` entries turned by the token's angles, forward or back."""
+        c, s_ = self._table(table)
+        t = self._turn(rows.to(self.cd).view(rows.shape[0], heads, width), c, -s_ if back else s_, dims, interleaved)
+        rows.copy_(t.reshape(rows.shape).to(rows.dtype))
 
     def paged_attention_streams(self, q, num_heads, num_kv_heads, head_dim, value_head_dim, k_pages, v_pages, block_tables, cu_q,
                                 seq_lens, out, scale, window, out_table, out_interleaved, max_q_len=0, max_seq_len=0):

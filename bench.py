@@ -685,7 +685,7 @@ class DesignTimer(KernelClassTimer):
         elif name == "moe_linear":
             x, w, out = a[0], a[1], a[5]
             experts = min(w.shape[0], out.shape[0])           # experts whose matrices a step has to read at the least
-            cls, tf, by = "products", 2 * out.shape[0] * w.shape[1] * w.shape[2], experts * w.shape[1] * w.shape[2] * w.element_size()
+            cls, tf, by = "experts", 2 * out.shape[0] * w.shape[1] * w.shape[2], experts * w.shape[1] * w.shape[2] * w.element_size()
         elif name in ("linear", "linear_residual_norm"):
             x, w = a[0], a[1]
             cls = "lm_head" if w.shape[0] == self.vocab else "products"

@@ -196,13 +196,15 @@ moe_linear_kernel(const TA* __restrict__ x, const TW* __restrict__ w, const int*
 // ------------------------------------------------------------------------------------------
 // The grouped product on tensor cores (bfloat16 operands, float32 accumulation): mma.sync m16n8k16.  A CTA of four
 // warps is a tile of MM_ROWS rows of one expert by MM_COLS outputs (GATED: the gate and the up column of each output,
-// so that the activation is the epilogue); warp w owns rows 16 w .. 16 w + 15 of the tile.  The k range is walked in
-// steps of MM_K through two stages of shared memory filled by 16-byte asynchronous copies (rows gathered through the
-// pair list; rows and columns beyond the tile, and k beyond the end, are filled with zeros), fragments come out of
-// shared memory by ldmatrix from rows padded to 80 bytes (no bank conflicts).  A row's result depends on its own
+// so that the activation is the epilogue); warp w owns rows 32 w .. 32 w + 31 of the tile, so that a weight fragment
+// read from shared memory serves two blocks of rows.  The k range is walked in steps of MM_K through three stages of
+// shared memory filled by 16-byte asynchronous copies (rows gathered through the pair list; rows and columns beyond
+// the tile, and k beyond the end, are filled with zeros), fragments come out of shared memory by ldmatrix from rows
+// padded to 80 bytes (no bank conflicts).  A row's result depends on its own
 // operands only, whatever else shares its tile.  k must be a multiple of 8.
 // ------------------------------------------------------------------------------------------
-constexpr int MM_ROWS = 64, MM_COLS = 64, MM_K = 32, MM_PAD = 8, MM_THREADS = 128;
+constexpr int MM_ROWS = 128, MM_COLS = 64, MM_K = 32, MM_PAD = 8, MM_THREADS = 128, MM_STAGES = 3;
+constexpr int MM_LD = MM_K + MM_PAD;
 
 __device__ __forceinline__ void mm_cp16(void* dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -219,14 +221,19 @@ __device__ __forceinline__ void mm_mma(float* c, const unsigned* a, unsigned b0,
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+template <bool GATED> constexpr size_t mm_smem_bytes() {
+  return (size_t)MM_STAGES * (MM_ROWS + (GATED ? 2 : 1) * MM_COLS) * MM_LD * sizeof(__nv_bfloat16) + MM_ROWS * sizeof(int);
+}
+
 template <typename TO, bool GATED>
 __global__ void __launch_bounds__(MM_THREADS)
 moe_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
                       const int* __restrict__ perm, int top, TO* __restrict__ out, int experts, int o, int k) {
   constexpr int WR = (GATED ? 2 : 1) * MM_COLS;              // weight rows of a tile
-  __shared__ __align__(16) __nv_bfloat16 As[2][MM_ROWS][MM_K + MM_PAD];
-  __shared__ __align__(16) __nv_bfloat16 Ws[2][WR][MM_K + MM_PAD];
-  __shared__ int src[MM_ROWS];
+  extern __shared__ __align__(16) unsigned char mm_raw[];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(mm_raw);                  // [STAGES][MM_ROWS][MM_LD]
+  __nv_bfloat16* Ws = As + (size_t)MM_STAGES * MM_ROWS * MM_LD;                  // [STAGES][WR][MM_LD]
+  int* src = reinterpret_cast<int*>(Ws + (size_t)MM_STAGES * WR * MM_LD);        // [MM_ROWS]
   ifb_pdl_wait();
   ifb_pdl_trigger();
   int e = 0, row0 = 0, row1 = 0, tile = blockIdx.y;
@@ -241,73 +248,81 @@ moe_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   const int col0 = blockIdx.x * MM_COLS;
   const int o_w = GATED ? 2 * o : o;
   const __nv_bfloat16* we = w + (size_t)e * o_w * k;
-  if (threadIdx.x < MM_ROWS) {
-    const int i = row0 + threadIdx.x;
-    src[threadIdx.x] = i < row1 ? (perm ? perm[i] / top : i) : -1;
+  for (int r = threadIdx.x; r < MM_ROWS; r += MM_THREADS) {
+    const int i = row0 + r;
+    src[r] = i < row1 ? (perm ? perm[i] / top : i) : -1;
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool warp_live = row0 + 16 * warp < row1;           // a warp whose 16 rows lie beyond the expert's rows only copies
+  // warp w owns rows 32 w .. 32 w + 31 of the tile, as two blocks of 16; a block beyond the expert's rows is not multiplied
+  const bool live0 = row0 + 32 * warp < row1, live1 = row0 + 32 * warp + 16 < row1;
   auto fill = [&](int stage, int k0) {
+    __nv_bfloat16* A = As + (size_t)stage * MM_ROWS * MM_LD;
+    __nv_bfloat16* W = Ws + (size_t)stage * WR * MM_LD;
     for (int idx = threadIdx.x; idx < MM_ROWS * (MM_K / 8); idx += MM_THREADS) {
       const int r = idx / (MM_K / 8), c = (idx % (MM_K / 8)) * 8;
       const int s = src[r];
       const bool ok = s >= 0 && k0 + c < k;
-      mm_cp16(&As[stage][r][c], ok ? x + (size_t)s * k + k0 + c : x, ok);
+      mm_cp16(A + r * MM_LD + c, ok ? x + (size_t)s * k + k0 + c : x, ok);
     }
     for (int idx = threadIdx.x; idx < WR * (MM_K / 8); idx += MM_THREADS) {
       const int r = idx / (MM_K / 8), c = (idx % (MM_K / 8)) * 8;
       const int half = r / MM_COLS, feat = col0 + r % MM_COLS;
       const bool ok = feat < o && k0 + c < k;
-      mm_cp16(&Ws[stage][r][c], ok ? we + ((size_t)half * o + feat) * k + k0 + c : we, ok);
+      mm_cp16(W + r * MM_LD + c, ok ? we + ((size_t)half * o + feat) * k + k0 + c : we, ok);
     }
-    asm volatile("cp.async.commit_group;\n" ::);
   };
-  float acc[MM_COLS / 8][4] = {}, up[GATED ? MM_COLS / 8 : 1][4] = {};
+  float acc[2][MM_COLS / 8][4] = {}, up[GATED ? 2 : 1][GATED ? MM_COLS / 8 : 1][4] = {};
   const int steps = (k + MM_K - 1) / MM_K;
-  fill(0, 0);
+  for (int p = 0; p < MM_STAGES - 1; ++p) {
+    if (p < steps) fill(p, p * MM_K);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
   for (int st = 0; st < steps; ++st) {
-    if (st + 1 < steps) {
-      fill((st + 1) & 1, (st + 1) * MM_K);
-      asm volatile("cp.async.wait_group 1;\n" ::);
-    } else {
-      asm volatile("cp.async.wait_group 0;\n" ::);
-    }
-    __syncthreads();
-    const int cur = st & 1;
-    if (warp_live) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(MM_STAGES - 2));      // stage st has landed
+    __syncthreads();                                                       // ... for everyone, and everyone is done with stage st - 1
+    if (st + MM_STAGES - 1 < steps) fill((st + MM_STAGES - 1) % MM_STAGES, (st + MM_STAGES - 1) * MM_K);
+    asm volatile("cp.async.commit_group;\n" ::);
+    if (!live0) continue;
+    const __nv_bfloat16* A = As + (size_t)(st % MM_STAGES) * MM_ROWS * MM_LD;
+    const __nv_bfloat16* W = Ws + (size_t)(st % MM_STAGES) * WR * MM_LD;
 #pragma unroll
-      for (int kk = 0; kk < MM_K; kk += 16) {
-        unsigned a[4];
-        mm_ldmatrix4(a[0], a[1], a[2], a[3], &As[cur][16 * warp + (lane & 15)][kk + (lane >> 4) * 8]);
+    for (int kk = 0; kk < MM_K; kk += 16) {
+      unsigned a0[4], a1[4] = {0u, 0u, 0u, 0u};
+      mm_ldmatrix4(a0[0], a0[1], a0[2], a0[3], A + (32 * warp + (lane & 15)) * MM_LD + kk + (lane >> 4) * 8);
+      if (live1) mm_ldmatrix4(a1[0], a1[1], a1[2], a1[3], A + (32 * warp + 16 + (lane & 15)) * MM_LD + kk + (lane >> 4) * 8);
 #pragma unroll
-        for (int nt = 0; nt < MM_COLS / 8; nt += 2) {
-          unsigned b0, b1, b2, b3;
-          const int brow = nt * 8 + (lane & 7) + (lane >> 4) * 8, bcol = kk + ((lane >> 3) & 1) * 8;
-          mm_ldmatrix4(b0, b1, b2, b3, &Ws[cur][brow][bcol]);
-          mm_mma(acc[nt], a, b0, b1);
-          mm_mma(acc[nt + 1], a, b2, b3);
-          if (GATED) {
-            mm_ldmatrix4(b0, b1, b2, b3, &Ws[cur][MM_COLS + brow][bcol]);
-            mm_mma(up[nt], a, b0, b1);
-            mm_mma(up[nt + 1], a, b2, b3);
-          }
+      for (int nt = 0; nt < MM_COLS / 8; nt += 2) {
+        unsigned b0, b1, b2, b3;
+        const int brow = nt * 8 + (lane & 7) + (lane >> 4) * 8, bcol = kk + ((lane >> 3) & 1) * 8;
+        mm_ldmatrix4(b0, b1, b2, b3, W + brow * MM_LD + bcol);
+        mm_mma(acc[0][nt], a0, b0, b1);
+        mm_mma(acc[0][nt + 1], a0, b2, b3);
+        if (live1) { mm_mma(acc[1][nt], a1, b0, b1); mm_mma(acc[1][nt + 1], a1, b2, b3); }
+        if (GATED) {
+          mm_ldmatrix4(b0, b1, b2, b3, W + (MM_COLS + brow) * MM_LD + bcol);
+          mm_mma(up[0][nt], a0, b0, b1);
+          mm_mma(up[0][nt + 1], a0, b2, b3);
+          if (live1) { mm_mma(up[GATED ? 1 : 0][nt], a1, b0, b1); mm_mma(up[GATED ? 1 : 0][nt + 1], a1, b2, b3); }
         }
       }
     }
-    __syncthreads();
   }
-  if (!warp_live) return;
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  if (!live0) return;
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-  for (int nt = 0; nt < MM_COLS / 8; ++nt) {
+  for (int blk = 0; blk < 2; ++blk) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = row0 + 16 * warp + g + (i >> 1) * 8, feat = col0 + nt * 8 + 2 * t + (i & 1);
-      if (row >= row1 || feat >= o) continue;
-      float y = acc[nt][i];
-      if (GATED) y = y / (1.f + expf(-y)) * up[nt][i];
-      out[(size_t)row * o + feat] = from_f32<TO>(y);
+    for (int nt = 0; nt < MM_COLS / 8; ++nt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = row0 + 32 * warp + 16 * blk + g + (i >> 1) * 8, feat = col0 + nt * 8 + 2 * t + (i & 1);
+        if (row >= row1 || feat >= o) continue;
+        float y = acc[blk][nt][i];
+        if (GATED) y = y / (1.f + expf(-y)) * up[GATED ? blk : 0][GATED ? nt : 0][i];
+        out[(size_t)row * o + feat] = from_f32<TO>(y);
+      }
     }
   }
 }
@@ -317,11 +332,14 @@ static int mm_launch(const void* x, const void* w, const int* offsets, const int
                      int o, int k, int gated, cudaStream_t s) {
   dim3 grid((o + MM_COLS - 1) / MM_COLS, (rows + MM_ROWS - 1) / MM_ROWS + experts);
   if (grid.y > 65535) return IFB_ERR_SIZE;
-  if (gated)
-    return ifb_launch(moe_linear_mma_kernel<TO, true>, grid, dim3(MM_THREADS), 0, s, (const __nv_bfloat16*)x,
+  if (gated) {
+    IFB_ALLOW_SMEM((moe_linear_mma_kernel<TO, true>), mm_smem_bytes<true>());
+    return ifb_launch(moe_linear_mma_kernel<TO, true>, grid, dim3(MM_THREADS), mm_smem_bytes<true>(), s, (const __nv_bfloat16*)x,
                       (const __nv_bfloat16*)w, offsets, perm, top, (TO*)out, experts, o, k);
-  return ifb_launch(moe_linear_mma_kernel<TO, false>, grid, dim3(MM_THREADS), 0, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                    offsets, perm, top, (TO*)out, experts, o, k);
+  }
+  IFB_ALLOW_SMEM((moe_linear_mma_kernel<TO, false>), mm_smem_bytes<false>());
+  return ifb_launch(moe_linear_mma_kernel<TO, false>, grid, dim3(MM_THREADS), mm_smem_bytes<false>(), s, (const __nv_bfloat16*)x,
+                    (const __nv_bfloat16*)w, offsets, perm, top, (TO*)out, experts, o, k);
 }
 
 template <typename TA, typename TW, typename TO>

@@ -862,6 +862,100 @@ def time_design_kernels(args):
     return 0
 
 
+def time_hybrid_kernels(args):
+    """Lunelorn's own kernels alone, on tensors made on the device at the sizes of hybrid_config: the experts' grouped
+    products (2,048 tokens, and a decode step of 8), the matrix-state recurrence in retention's and in time mixing's form
+    and the minGRU (a 2,048-token prompt; a decode step of 8 requests).  Microseconds by CUDA events over 20 calls after
+    3, with the fraction of the bound (tensor flops over the measured rate, float32 flops over the nominal 74.4 TFLOP/s,
+    bytes over the measured copy bandwidth, whichever is slowest); one JSON line.  (Also the small case for a profiler.)"""
+    import torch
+    from infurnace_b200.kernels import load_cuda_kernels
+    K = load_cuda_kernels()
+    hbm_peak, tc_peak, peak_src = read_peaks()
+    fp32_peak = torch.cuda.get_device_properties(0).multi_processor_count * FP32_LANES_PER_SM * 2 * 1.965 / 1e3
+    g = torch.Generator(device="cuda").manual_seed(1)
+    rnd = lambda *shape, dtype=torch.float32: torch.randn(*shape, generator=g, device="cuda").to(dtype)      # noqa: E731
+
+    def timed(f, reps=20):
+        for _ in range(3):
+            f()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            f()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / reps * 1e3
+
+    def entry(us, tf=0.0, ff=0.0, by=0.0):
+        bound = max(tf / (tc_peak * 1e12), ff / (fp32_peak * 1e12), by / (hbm_peak * 1e9)) * 1e6
+        return {"us": round(us, 1), "of_bound": round(bound / us, 4)}
+
+    def step_arrays(lens_new):
+        cu = torch.tensor([0] + list(torch.tensor(lens_new).cumsum(0)), dtype=torch.int32, device="cuda")
+        return cu, torch.tensor([n + 5 for n in lens_new], dtype=torch.int32, device="cuda"), \
+            torch.arange(len(lens_new), dtype=torch.int32, device="cuda")
+
+    out = {}
+    for size in args.design_sizes.split(","):
+        conf = hybrid_config(size)
+        W = conf["width"]
+        ret = next(l["mixer"] for l in conf["layers"] if l["type"] == "retention")
+        mix = next(l["mixer"] for l in conf["layers"] if l["type"] == "wkv")
+        unit = next(l["mixer"]["right"]["width"] for l in conf["layers"] if l["type"] == "parallel")
+        mlp = conf["layers"][0]["mlp"]
+        E, top, ff = mlp["router"]["experts"], mlp["router"]["top"], mlp["expert"]["ff"]
+        r = {}
+        w1, w2 = rnd(E, 2 * ff, W, dtype=torch.bfloat16) / 32, rnd(E, W, ff, dtype=torch.bfloat16) / 32
+        for label, n in (("prompt_2048", 2048), ("decode_8", 8)):
+            pairs = n * top
+            h, logits = rnd(n, W, dtype=torch.bfloat16), rnd(n, E)
+            ids, gates = torch.zeros(n, top, dtype=torch.int32, device="cuda"), torch.zeros(n, top, device="cuda")
+            off, perm, pos = (torch.zeros(E + 1, dtype=torch.int32, device="cuda"), torch.zeros(pairs, dtype=torch.int32, device="cuda"),
+                              torch.zeros(pairs, dtype=torch.int32, device="cuda"))
+            act, y = torch.zeros(pairs, ff, dtype=torch.bfloat16, device="cuda"), torch.zeros(pairs, W, device="cuda")
+            delta = torch.zeros(n, W, device="cuda")
+            used = min(E, pairs)
+            r["experts_" + label] = {
+                "route_and_list": entry(timed(lambda: (K.moe_route(logits, top, ids, gates), K.moe_plan(ids, E, off, perm, pos)))),
+                "gate_up": entry(timed(lambda: K.moe_linear(h, w1, off, perm, top, act, epilogue="silu_gate")),
+                                 tf=2.0 * pairs * 2 * ff * W, by=used * 2 * ff * W * 2),
+                "down": entry(timed(lambda: K.moe_linear(act, w2, off, None, 1, y)), tf=2.0 * pairs * ff * W, by=used * ff * W * 2),
+                "sum": entry(timed(lambda: K.moe_combine(y, pos, gates, delta)), by=pairs * W * 4 + n * W * 4)}
+        for form, heads, dim, vdim in (("retention", ret["heads"], ret["dim"], ret["vdim"]), ("time_mixing", mix["heads"], mix["dim"], mix["dim"])):
+            hd, hv = heads * dim, heads * vdim
+            state = torch.zeros(8, heads, dim, vdim, device="cuda")
+            for label, lens in (("prompt_2048", [2048]), ("decode_8", [1] * 8)):
+                n = sum(lens)
+                cu, seq, slots = step_arrays(lens)
+                q, k, v, gate, wraw = rnd(n, hd), rnd(n, hd), rnd(n, hv), rnd(n, hv), rnd(n, hd)
+                o = torch.zeros(n, hv, dtype=torch.bfloat16, device="cuda")
+                if form == "retention":
+                    decay = torch.full((heads,), 0.97, device="cuda")
+                    f = lambda: K.linear_scan(q, k, v, None, heads, dim, vdim, state, slots, cu, seq, o, 1e-6, decay=decay,      # noqa: E731
+                                              key_scale=dim ** -0.5, gate=gate, max_q_len=max(lens))
+                else:
+                    w0, u, nw = rnd(hd) - 1.5, rnd(hd) / 2, 1 + rnd(hv) / 5
+                    f = lambda: K.linear_scan(q, k, v, wraw, heads, dim, vdim, state, slots, cu, seq, o, 1e-6, w_bias=w0, bonus=u,      # noqa: E731
+                                              norm_weight=nw, gate=gate, max_q_len=max(lens))
+                r[f"{form}_{label}"] = entry(timed(f), ff=6.0 * n * heads * dim * vdim,
+                                             by=n * (3 * hd + 2 * hv) * 4 + n * hv * 2 + 2 * len(lens) * heads * dim * vdim * 4)
+                state.zero_()
+        ustate, zb, xb = torch.zeros(8, unit, device="cuda"), rnd(unit), rnd(unit)
+        for label, lens in (("prompt_2048", [2048]), ("decode_8", [1] * 8)):
+            n = sum(lens)
+            cu, seq, slots = step_arrays(lens)
+            proj, o = rnd(n, 3 * unit), torch.zeros(n, unit, dtype=torch.bfloat16, device="cuda")
+            r["gated_unit_" + label] = entry(timed(lambda: K.gated_unit_scan(proj, zb, xb, ustate, slots, cu, seq, o, max_q_len=max(lens))),
+                                             ff=10.0 * n * unit, by=n * unit * 14)
+        out[size] = r
+    K.check_device_errors()
+    print(json.dumps({"metric": "hybrid_kernels_alone", "dtype": "bfloat16 operands, float32 recurrences", "peaks": {
+        "hbm_gbs": hbm_peak, "tensor_tflops": tc_peak, "fp32_tflops_nominal": round(fp32_peak, 1), "source": peak_src}, "sizes": out}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -895,7 +989,9 @@ def main():
         return 2
     args.warmup = max(3, args.warmup)
     if args.designs:
-        return time_design_kernels(args) if args.kernels_alone else run_designs(args)
+        if args.kernels_alone:
+            return time_hybrid_kernels(args) if args.hybrid else time_design_kernels(args)
+        return run_designs(args)
     return run_ours(args)
 
 

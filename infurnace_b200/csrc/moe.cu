@@ -327,6 +327,118 @@ moe_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   }
 }
 
+// The same product for steps of few rows (decode): tiles of SK_ROWS rows, so that the step is the experts' weights
+// streamed once; the four warps of a CTA split the tile's 64 outputs, the k range goes through four stages of 128, which
+// keeps about a hundred kilobytes of weights in flight per CTA (a CTA of the wide form waits on 16 KB at a time).
+constexpr int MM_SKINNY_MAX_ROWS = 256;      // rows of a step up to which the few-rows form runs
+constexpr int SK_ROWS = 16, SK_COLS = 64, SK_K = 128, SK_STAGES = 4, SK_LD = SK_K + 8, SK_THREADS = 128;
+
+template <bool GATED> constexpr size_t sk_smem_bytes() {
+  return (size_t)SK_STAGES * (SK_ROWS + (GATED ? 2 : 1) * SK_COLS) * SK_LD * sizeof(__nv_bfloat16) + SK_ROWS * sizeof(int);
+}
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(SK_THREADS)
+moe_linear_mma_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
+                             const int* __restrict__ perm, int top, TO* __restrict__ out, int experts, int o, int k) {
+  constexpr int WR = (GATED ? 2 : 1) * SK_COLS;
+  extern __shared__ __align__(16) unsigned char mm_raw[];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(mm_raw);                  // [STAGES][SK_ROWS][SK_LD]
+  __nv_bfloat16* Ws = As + (size_t)SK_STAGES * SK_ROWS * SK_LD;                  // [STAGES][WR][SK_LD]
+  int* src = reinterpret_cast<int*>(Ws + (size_t)SK_STAGES * WR * SK_LD);        // [SK_ROWS]
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  int e = 0, row0 = 0, row1 = 0, tile = blockIdx.y;
+  bool found = false;
+  for (; e < experts; ++e) {
+    const int a = offsets[e], b = offsets[e + 1];
+    const int tiles = (b - a + SK_ROWS - 1) / SK_ROWS;
+    if (tile < tiles) { row0 = a + tile * SK_ROWS; row1 = min(b, row0 + SK_ROWS); found = true; break; }
+    tile -= tiles;
+  }
+  if (!found) return;
+  const int col0 = blockIdx.x * SK_COLS;
+  const int o_w = GATED ? 2 * o : o;
+  const __nv_bfloat16* we = w + (size_t)e * o_w * k;
+  if (threadIdx.x < SK_ROWS) {
+    const int i = row0 + threadIdx.x;
+    src[threadIdx.x] = i < row1 ? (perm ? perm[i] / top : i) : -1;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  auto fill = [&](int stage, int k0) {
+    __nv_bfloat16* A = As + (size_t)stage * SK_ROWS * SK_LD;
+    __nv_bfloat16* W = Ws + (size_t)stage * WR * SK_LD;
+    for (int idx = threadIdx.x; idx < SK_ROWS * (SK_K / 8); idx += SK_THREADS) {
+      const int r = idx / (SK_K / 8), c = (idx % (SK_K / 8)) * 8;
+      const int s = src[r];
+      const bool ok = s >= 0 && k0 + c < k;
+      mm_cp16(A + r * SK_LD + c, ok ? x + (size_t)s * k + k0 + c : x, ok);
+    }
+    for (int idx = threadIdx.x; idx < WR * (SK_K / 8); idx += SK_THREADS) {
+      const int r = idx / (SK_K / 8), c = (idx % (SK_K / 8)) * 8;
+      const int half = r / SK_COLS, feat = col0 + r % SK_COLS;
+      const bool ok = feat < o && k0 + c < k;
+      mm_cp16(W + r * SK_LD + c, ok ? we + ((size_t)half * o + feat) * k + k0 + c : we, ok);
+    }
+  };
+  float acc[2][4] = {}, up[2][4] = {};
+  const int steps = (k + SK_K - 1) / SK_K;
+  for (int p = 0; p < SK_STAGES - 1; ++p) {
+    if (p < steps) fill(p, p * SK_K);
+    asm volatile("cp.async.commit_group;\n" ::);
+  }
+  for (int st = 0; st < steps; ++st) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(SK_STAGES - 2));
+    __syncthreads();
+    if (st + SK_STAGES - 1 < steps) fill((st + SK_STAGES - 1) % SK_STAGES, (st + SK_STAGES - 1) * SK_K);
+    asm volatile("cp.async.commit_group;\n" ::);
+    const __nv_bfloat16* A = As + (size_t)(st % SK_STAGES) * SK_ROWS * SK_LD;
+    const __nv_bfloat16* W = Ws + (size_t)(st % SK_STAGES) * WR * SK_LD;
+#pragma unroll
+    for (int kk = 0; kk < SK_K; kk += 16) {
+      unsigned a[4], b0, b1, b2, b3;
+      mm_ldmatrix4(a[0], a[1], a[2], a[3], A + (lane & 15) * SK_LD + kk + (lane >> 4) * 8);
+      const int brow = 16 * warp + (lane & 7) + (lane >> 4) * 8, bcol = kk + ((lane >> 3) & 1) * 8;
+      mm_ldmatrix4(b0, b1, b2, b3, W + brow * SK_LD + bcol);
+      mm_mma(acc[0], a, b0, b1);
+      mm_mma(acc[1], a, b2, b3);
+      if (GATED) {
+        mm_ldmatrix4(b0, b1, b2, b3, W + (SK_COLS + brow) * SK_LD + bcol);
+        mm_mma(up[0], a, b0, b1);
+        mm_mma(up[1], a, b2, b3);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = row0 + g + (i >> 1) * 8, feat = col0 + 16 * warp + nt * 8 + 2 * t + (i & 1);
+      if (row >= row1 || feat >= o) continue;
+      float y = acc[nt][i];
+      if (GATED) y = y / (1.f + expf(-y)) * up[nt][i];
+      out[(size_t)row * o + feat] = from_f32<TO>(y);
+    }
+  }
+}
+
+template <typename TO>
+static int sk_launch(const void* x, const void* w, const int* offsets, const int* perm, int top, void* out, int rows, int experts,
+                     int o, int k, int gated, cudaStream_t s) {
+  dim3 grid((o + SK_COLS - 1) / SK_COLS, (rows + SK_ROWS - 1) / SK_ROWS + experts);
+  if (gated) {
+    IFB_ALLOW_SMEM((moe_linear_mma_skinny_kernel<TO, true>), sk_smem_bytes<true>());
+    return ifb_launch(moe_linear_mma_skinny_kernel<TO, true>, grid, dim3(SK_THREADS), sk_smem_bytes<true>(), s,
+                      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, offsets, perm, top, (TO*)out, experts, o, k);
+  }
+  IFB_ALLOW_SMEM((moe_linear_mma_skinny_kernel<TO, false>), sk_smem_bytes<false>());
+  return ifb_launch(moe_linear_mma_skinny_kernel<TO, false>, grid, dim3(SK_THREADS), sk_smem_bytes<false>(), s,
+                    (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, offsets, perm, top, (TO*)out, experts, o, k);
+}
+
 template <typename TO>
 static int mm_launch(const void* x, const void* w, const int* offsets, const int* perm, int top, void* out, int rows, int experts,
                      int o, int k, int gated, cudaStream_t s) {
@@ -363,8 +475,13 @@ IFB_EXPORT int ifb_moe_linear(const void* x, int x_dtype, const void* w, int w_d
   if (rows <= 0 || o <= 0) return IFB_OK;
   if (experts < 1 || k < 1 || top < 1) return IFB_ERR_SIZE;
   if (tensor_cores && x_dtype == IFB_BF16 && w_dtype == IFB_BF16 && k % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0)) {
-    if (out_dtype == IFB_F32) return mm_launch<float>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
-    if (out_dtype == IFB_BF16) return mm_launch<__nv_bfloat16>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+    const bool few = rows <= MM_SKINNY_MAX_ROWS;          // a step of few rows: tiles of 16 rows and a deep pipeline
+    if (out_dtype == IFB_F32)
+      return few ? sk_launch<float>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream)
+                 : mm_launch<float>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
+    if (out_dtype == IFB_BF16)
+      return few ? sk_launch<__nv_bfloat16>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream)
+                 : mm_launch<__nv_bfloat16>(x, w, offsets, perm, top, out, rows, experts, o, k, gated, stream);
     return IFB_ERR_DTYPE;
   }
 #define ML_CASE(XD, WD, OD, TA, TW, TO)                                                                      \

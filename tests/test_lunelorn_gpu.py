@@ -17,17 +17,31 @@ BF16_TOL = 4e-2      # times the largest logit: activations between kernels carr
 BF16_SHARE = 0.7     # of the positions: a bfloat16 rounding can turn an expert choice, which the plain implementation does not follow
 
 
-def rows_match(out, want, dtype, what=""):
-    """float32: every position within F32_TOL of the largest logit.  bfloat16: BF16_SHARE of the positions within BF16_TOL of
+def float32_noise(cfg, w, toks):
+    """Per position, how far the plain implementation itself moves when it is computed in float32: where a position is
+    ill-conditioned (a sublayer's result near zero before its unit norm, say) no float32 engine can be closer."""
+    P.F = torch.float32
+    try:
+        low = P.forward(cfg, w, toks).double()
+    finally:
+        P.F = torch.float64
+    return (low - P.forward(cfg, w, toks)).abs().max(dim=-1).values
+
+
+def rows_match(out, want, dtype, what="", noise=None, share=None):
+    """float32: every position within F32_TOL of the largest logit (or, with ``noise``, within three times the plain
+    implementation's own float32 movement there, if that is more).  bfloat16: BF16_SHARE of the positions within BF16_TOL of
     it, and the median within three quarters of it (the float32 runs are the sharp test of every mechanism; these show
     that the bfloat16 path computes the same model)."""
     top = max(1.0, float(want.abs().max()))
     err = (out.double() - want.double()).abs().max(dim=-1).values
     if dtype in ("float32", torch.float32):
-        assert float(err.max()) <= F32_TOL * top, f"{what}: position {int(err.argmax())}: {float(err.max())} > {F32_TOL * top}"
+        tol = torch.full_like(err, F32_TOL * top) if noise is None else torch.maximum(torch.full_like(err, F32_TOL * top), 3 * noise)
+        bad = err > tol
+        assert not bool(bad.any()), f"{what}: position {int(bad.nonzero()[0])}: {float(err[bad][0])} > {float(tol[bad][0])}"
     else:
         good = float((err <= BF16_TOL * top).double().mean())
-        assert good >= BF16_SHARE and float(err.median()) <= 0.75 * BF16_TOL * top, \
+        assert good >= (share or BF16_SHARE) and float(err.median()) <= (0.75 if share is None else 1.0) * BF16_TOL * top, \
             f"{what}: {good:.2f} of the positions within {BF16_TOL * top}, median {float(err.median())}; first look at {int(err.argmax())}"
     return float(err.max())
 
@@ -251,13 +265,22 @@ def _attention_case(K, H, G, d, dv, rot, inter, ps, dtype, lens_new, lens_old, w
             K.paged_attention_streams(q_got, H, G, d, dv, kp, vp, tables.cuda(), cu.cuda(), seq.cuda(), got, 0.3, window, vt.cuda(),
                                       inter, max_q_len=max(lens), max_seq_len=int(seq.max()))
             close(got, want, 1e-5 if dtype == torch.float32 else 0.05, "attention")
+            if both is not None and dtype == torch.bfloat16 and d % 16 == 0 and H // G <= 16:
+                # the route of bfloat16 steps with keys and values of one width: the framework's tensor-core attention on the
+                # entry's one tensor, the queries in a buffer of their own, then the turn back
+                got2 = torch.zeros(n, H * dv, device="cuda", dtype=dtype)
+                K.paged_attention(q_got, H, G, d, both, tables.cuda(), cu.cuda(), seq.cuda(), got2, 0.3, window, max(lens),
+                                  int(seq.max()), min_q_len=min(lens))
+                K.rotate_rows(got2, vt.cuda(), H, dv, dv, inter, back=True)
+                close(got2, want, 0.05, "attention on tensor cores")
             out_pair = (got, want)
     return out_pair
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,rot,inter,ps", [(4, 2, 16, 8, 8, False, 16), (6, 6, 8, 16, 8, False, 8), (8, 1, 128, 128, 32, False, 16),
-                                                    (3, 1, 24, 40, 12, True, 4), (2, 2, 64, 64, 0, False, 32), (5, 5, 256, 2, 256, False, 16)])
+                                                    (3, 1, 24, 40, 12, True, 4), (2, 2, 64, 64, 0, False, 32), (5, 5, 256, 2, 256, False, 16),
+                                                    (6, 2, 32, 32, 2, False, 16), (2, 2, 48, 48, 48, False, 16), (4, 4, 16, 16, 8, True, 16)])
 def test_rotated_values_attention_kernels(K, H, G, d, dv, rot, inter, ps, dtype):
     _attention_case(K, H, G, d, dv, rot, inter, ps, dtype, [33, 1, 2, 1], [0, 70, 15, 16])
     _attention_case(K, H, G, d, dv, rot, inter, ps, dtype, [5, 1], [40, 40], window=7, seed=1)
@@ -377,6 +400,47 @@ def test_cutting_modes(models, name, mode, dtype):
     else:         # the share of positions is taken over all requests (three of them have one to three tokens)
         worst = rows_match(torch.cat([out[rid] for rid in reqs]), torch.cat([ref[rid] for rid in reqs]), dtype, f"{name} {mode} {dtype}")
     print(f"{name} {mode} {dtype}: worst {worst:.3g} (largest logit {max(float(r.abs().max()) for r in ref.values()):.3g})")
+
+
+OTHER_SIZES = {
+    # width and feed-forward no multiple of 8 (the plain products), heads of 24 (no tensor-core attention), one expert, a loop
+    # over the middle layer only, no side input
+    "odd": TL._config(53, 100, 1e-5, [TL._ret(3, 12, 20, [0.3, 0.8, 0.99], TL._moe(1, 1, 36)),
+                                      TL._par(6, 2, 24, 24, 6, 777.0, 0.2, 33, 0.7, 1.4, TL._moe(5, 5, 20)),
+                                      TL._wkv(5, 20, 7, None)], loop=(1, 2, 2), cap=8.0),
+    # heads of 48 and of 32 with keys and values of one width (the tensor-core attention at those sizes), as many key heads
+    # as query heads and one for all, retention heads of 48 x 96, a loop over everything, side input of one column
+    "tc": TL._config(211, 96, 1e-6, [TL._par(2, 2, 48, 48, 48, 5000.0, 0.15, 8, 1.0, 0.5, TL._moe(6, 2, 24)),
+                                     TL._ret(2, 48, 96, [0.9, 0.999], None),
+                                     TL._par(6, 1, 32, 32, 2, 20.0, 0.25, 96, 0.5, 1.0, TL._moe(3, 1, 40)),
+                                     TL._wkv(3, 32, 16, TL._moe(2, 2, 8))], loop=(0, 4, 2), side=1),
+    # a single layer; a time-mixing layer alone with one head
+    "one": TL._config(40, 32, 1e-5, [TL._wkv(1, 32, 2, TL._moe(4, 3, 16))], side=5, cap=20.0),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(OTHER_SIZES))
+def test_other_sizes_and_orders(tmp_path, name, dtype):
+    """Models of other sizes, head counts, orders of layers and loops, in a mixed schedule over a small pool."""
+    from infurnace_b200.engine.loading import EngineOptions, build_runner
+    conf = OTHER_SIZES[name]
+    d = TL.make_model_dir("_" + name, str(tmp_path), config=conf, seed=31, store="bfloat16")
+    cfg, w = TL.load_model_dir(d)
+    reqs = {f"r{i}": tiny.random_tokens(cfg["vocab"], n, 7 + i) for i, n in enumerate([45, 130, 3, 70, 1, 99, 20])}
+    ref = {r: P.forward(cfg, w, t).float() for r, t in reqs.items()}
+    steps = tiny.schedule_mixed(reqs, max_live=4, max_tokens=384, seed=3)
+    runner = build_runner(d, EngineOptions(dtype=dtype, device="cuda", page_size=16, num_pages=24, max_num_seqs=4,
+                                           max_num_batched_tokens=384, max_model_len=384))[2]
+    out = tiny.collect(steps, tiny.run_inprocess(runner, steps), cfg["vocab"])
+    runner.rt.kernels.check_device_errors()
+    assert runner.cache.num_free_slots == 4 and runner.cache.free_pages() == [g.pool.num_pages for g in runner.cache.kv_groups]
+    if dtype == "float32":
+        for rid in reqs:
+            rows_match(out[rid], ref[rid], dtype, f"{name} request {rid}", noise=float32_noise(cfg, w, reqs[rid]))
+    else:
+        # these models are worse conditioned than the three above (see float32_noise); the kernels' own tests are the sharp ones
+        rows_match(torch.cat([out[r] for r in reqs]), torch.cat([ref[r] for r in reqs]), dtype, name, share=0.5)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

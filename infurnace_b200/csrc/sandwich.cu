@@ -7,7 +7,8 @@
 #include <math.h>
 
 // ------------------------------------------------------------------------------------------
-// x[n, :] += y[n, :] / sqrt(mean(y[n, :]^2) + eps) * post[:]
+// x[n, :] += y[n, :] / sqrt(mean(y[n, :]^2) + eps) * post[:],   y = s1 * y1 (+ s2 * y2: the weighted sum of two mixers
+// that ran side by side is formed here instead of in a launch of its own; s1 = 1 without y2 leaves y1 as it is)
 // out (may be null): what the next product reads, in the dtype TO:
 //     next given:  x[n, :] / sqrt(mean(x[n, :]^2) + eps) * next[:]      (the next sublayer's pre-norm)
 //     else         x[n, :]
@@ -17,26 +18,29 @@
 constexpr int RN_THREADS = 256, RN_KEEP = 8;
 template <typename TO>
 __global__ void __launch_bounds__(RN_THREADS)
-residual_norm_update_kernel(float* __restrict__ x, const float* __restrict__ y, const void* __restrict__ post, int post_dtype,
+residual_norm_update_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ y2, float s1, float s2,
+                            const void* __restrict__ post, int post_dtype,
                             const void* __restrict__ next, int next_dtype, float eps, TO* __restrict__ out, int hidden) {
   __shared__ float scratch[33];
   ifb_pdl_wait();
   ifb_pdl_trigger();
   const size_t base = (size_t)blockIdx.x * hidden;
   const float* yr = y + base;
+  const float* y2r = y2 ? y2 + base : nullptr;
   float* xr = x + base;
   const bool held = hidden <= RN_KEEP * RN_THREADS;
+  auto term = [&](int e) { return y2r ? fmaf(s2, y2r[e], s1 * yr[e]) : s1 * yr[e]; };
   float keep[RN_KEEP];
   float ss = 0.f;
   if (held) {
 #pragma unroll
     for (int j = 0; j < RN_KEEP; ++j) {
       const int e = threadIdx.x + j * RN_THREADS;
-      keep[j] = e < hidden ? yr[e] : 0.f;
+      keep[j] = e < hidden ? term(e) : 0.f;
       ss += keep[j] * keep[j];
     }
   } else {
-    for (int e = threadIdx.x; e < hidden; e += RN_THREADS) ss += yr[e] * yr[e];
+    for (int e = threadIdx.x; e < hidden; e += RN_THREADS) { const float v = term(e); ss += v * v; }
   }
   ss = block_sum(ss, scratch);
   const float ry = 1.f / sqrtf(ss / (float)hidden + eps);
@@ -53,7 +57,7 @@ residual_norm_update_kernel(float* __restrict__ x, const float* __restrict__ y, 
     }
   } else {
     for (int e = threadIdx.x; e < hidden; e += RN_THREADS) {
-      const float v = xr[e] + yr[e] * ry * load_as_f32(post, post_dtype, e);
+      const float v = xr[e] + term(e) * ry * load_as_f32(post, post_dtype, e);
       xr[e] = v;
       sx += v * v;
     }
@@ -77,18 +81,18 @@ residual_norm_update_kernel(float* __restrict__ x, const float* __restrict__ y, 
   }
 }
 
-IFB_EXPORT int ifb_residual_norm_update(float* x, const float* y, const void* post, int post_dtype, const void* next,
+IFB_EXPORT int ifb_residual_norm_update(float* x, const float* y, const float* y2, float s1, float s2, const void* post, int post_dtype, const void* next,
                                         int next_dtype, float eps, void* out, int out_dtype, int n, int hidden,
                                         cudaStream_t stream) {
   if (n <= 0 || hidden <= 0) return IFB_OK;
   if ((post_dtype != IFB_F32 && post_dtype != IFB_BF16) || (next && next_dtype != IFB_F32 && next_dtype != IFB_BF16))
     return IFB_ERR_DTYPE;
   if (out && out_dtype == IFB_BF16)
-    return ifb_launch(residual_norm_update_kernel<__nv_bfloat16>, dim3(n), dim3(RN_THREADS), 0, stream, x, y, post, post_dtype,
-                      next, next_dtype, eps, (__nv_bfloat16*)out, hidden);
+    return ifb_launch(residual_norm_update_kernel<__nv_bfloat16>, dim3(n), dim3(RN_THREADS), 0, stream, x, y, y2, s1, s2, post,
+                      post_dtype, next, next_dtype, eps, (__nv_bfloat16*)out, hidden);
   if (out && out_dtype != IFB_F32) return IFB_ERR_DTYPE;
-  return ifb_launch(residual_norm_update_kernel<float>, dim3(n), dim3(RN_THREADS), 0, stream, x, y, post, post_dtype, next,
-                    next_dtype, eps, (float*)out, hidden);
+  return ifb_launch(residual_norm_update_kernel<float>, dim3(n), dim3(RN_THREADS), 0, stream, x, y, y2, s1, s2, post, post_dtype,
+                    next, next_dtype, eps, (float*)out, hidden);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -851,8 +851,8 @@ class CudaKernels:
     def _hyb_lib(self):
         if self._hyb is None:
             m = self._hyb = load_library("hybrid", progress=self._progress)
-            m.ifb_residual_norm_update.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int,
-                                                   c_int, c_int, c_void_p]
+            m.ifb_residual_norm_update.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_int, c_void_p, c_int,
+                                                   c_float, c_void_p, c_int, c_int, c_int, c_void_p]
             m.ifb_add_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
             m.ifb_scaled_sum.argtypes = [c_void_p, c_void_p, c_float, c_int, c_longlong, c_void_p]
             m.ifb_token_side_gate.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
@@ -885,9 +885,10 @@ class CudaKernels:
             m.ifb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         return self._hyb
 
-    def residual_norm_update(self, x, y, post_weight, eps, out=None, next_weight=None):
+    def residual_norm_update(self, x, y, post_weight, eps, out=None, next_weight=None, y2=None, scale=1.0, scale2=1.0):
         """x += y / sqrt(mean(y^2) + eps) * post_weight, row by row in float32.  ``out``: the updated rows for the next
-        product in out's dtype: x / sqrt(mean(x^2) + eps) * next_weight, or x itself when next_weight is None."""
+        product in out's dtype: x / sqrt(mean(x^2) + eps) * next_weight, or x itself when next_weight is None.
+        With ``y2``, y stands for scale * y + scale2 * y2 (two mixers side by side), formed in the same pass."""
         _dense(x, "x", torch.float32), _dense(y, "y", torch.float32), _dense(post_weight, "post_weight")
         n, hidden = x.shape
         if y.shape != x.shape or post_weight.numel() != hidden:
@@ -896,9 +897,11 @@ class CudaKernels:
             raise KernelError("residual_norm_update: next_weight needs out and has the row's length")
         if out is not None and _dense(out, "out").shape != x.shape:
             raise KernelError("residual_norm_update: out has the shape of x")
+        if y2 is not None and _dense(y2, "y2", torch.float32).shape != x.shape:
+            raise KernelError("residual_norm_update: y2 has the shape of x")
         self.launches += 1
         _check(self._hyb_lib().ifb_residual_norm_update(
-            x.data_ptr(), y.data_ptr(), post_weight.data_ptr(), _code(post_weight), _ptr(next_weight),
+            x.data_ptr(), y.data_ptr(), _ptr(y2), float(scale), float(scale2), post_weight.data_ptr(), _code(post_weight), _ptr(next_weight),
             _code(next_weight) if next_weight is not None else 0, float(eps), _ptr(out), _code(out) if out is not None else 0,
             n, hidden, self._stream()), "residual_norm_update")
 

@@ -4,6 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..config.specs import PostNormBlockSpec, PreNormBlockSpec, SandwichBlockSpec, StreamInjectSpec, TokenSideSpec
+from .parallel import WeightedSum
 from .registry import Folded, build_part, register_part
 
 
@@ -175,8 +176,12 @@ class SandwichBlock:
         out = None
         if then_norm is not None or then_copy:
             out = ctx.buffer("h", x.shape, self.rt.act_dtype)
-        self.k.residual_norm_update(x, y, post.weight, post.spec.eps, out=out,
-                                    next_weight=then_norm.weight if then_norm is not None else None)
+        nxt = then_norm.weight if then_norm is not None else None
+        if isinstance(y, WeightedSum):               # two mixers side by side: their weighted sum is formed in this pass
+            (y1, s1), (y2, s2) = y.terms
+            self.k.residual_norm_update(x, y1, post.weight, post.spec.eps, out=out, next_weight=nxt, y2=y2, scale=s1, scale2=s2)
+        else:
+            self.k.residual_norm_update(x, y, post.weight, post.spec.eps, out=out, next_weight=nxt)
         return out
 
     def forward(self, x, pending, ctx, call):
@@ -186,7 +191,10 @@ class SandwichBlock:
             x.add_(pending)
         h = ctx.buffer("h", x.shape, self.rt.act_dtype)
         self.mixer_norm.forward(x, h)
-        y = self.mixer.forward(h, ctx, call)
+        if getattr(self.mixer, "can_return_weighted", False):
+            y = self.mixer.forward(h, ctx, call, weighted=True)
+        else:
+            y = self.mixer.forward(h, ctx, call)
         if self.ffn is not None:
             h = self._update(x, y, self.mixer_post, ctx, then_norm=self.ffn_norm)
             y = self.ffn.forward(h, ctx)

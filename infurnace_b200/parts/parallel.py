@@ -7,9 +7,20 @@ from ..config.specs import LayerCall, ParallelMixerSpec
 from .registry import build_part, register_part
 
 
+class WeightedSum:
+    """The results of mixers that ran side by side, not yet added up: ``terms`` = [(float32 tensor, scale), ...].  A
+    block whose stream update can form the sum in its own pass asks for this (``weighted=True``)."""
+    __slots__ = ("terms",)
+
+    def __init__(self, terms):
+        self.terms = terms
+
+
 class ParallelMixer:
     """h -> sum_i scales[i] * mixers[i](h).  Mixer i keeps cache entry ``(call.cache, i)``.  The weighted sum is one
-    small kernel over the mixers' float32 results."""
+    small kernel per mixer over their float32 results, unless the caller takes a :class:`WeightedSum` of two."""
+
+    can_return_weighted = True
 
     def __init__(self, spec: ParallelMixerSpec, weights, runtime):
         self.spec = spec
@@ -21,11 +32,12 @@ class ParallelMixer:
     def graph_safe(self):
         return all(getattr(m, "graph_safe", False) for m in self.mixers)
 
-    def forward(self, h, ctx, call):
-        n = h.shape[0]
+    def forward(self, h, ctx, call, weighted=False):
+        results = [mixer.forward(h, ctx, LayerCall(call.layer, (call.cache, i), call.store)) for i, mixer in enumerate(self.mixers)]
+        if weighted and len(results) == 2 and results[0].data_ptr() != results[1].data_ptr():
+            return WeightedSum(list(zip(results, self.spec.scales)))
         total = None
-        for i, (mixer, scale) in enumerate(zip(self.mixers, self.spec.scales)):
-            d = mixer.forward(h, ctx, LayerCall(call.layer, (call.cache, i), call.store))
+        for d, scale in zip(results, self.spec.scales):
             if total is None:
                 total = ctx.buffer("delta_parallel", d.shape, torch.float32)
                 self.k.scaled_sum(total, d, scale, accumulate=False)

@@ -290,10 +290,12 @@ class ReferenceKernels:
                 out[t] = o.to(out.dtype)
 
     # ------------------------------------------------------------------ sandwich-norm blocks, loops, token side input
-    def residual_norm_update(self, x, y, post_weight, eps, out=None, next_weight=None):
-        """x += y / sqrt(mean(y^2) + eps) * post_weight (float32, in place).  ``out``: the updated rows for the next
+    def residual_norm_update(self, x, y, post_weight, eps, out=None, next_weight=None, y2=None, scale=1.0, scale2=1.0):
+        """x += y / sqrt(mean(y^2) + eps) * post_weight (float32, in place); with y2, y stands for scale * y + scale2 * y2.  ``out``: the updated rows for the next
         product, x / sqrt(mean(x^2) + eps) * next_weight, or x itself when next_weight is None, in out's dtype."""
-        v = y.to(self.cd)
+        v = y.to(self.cd) * scale
+        if y2 is not None:
+            v = v + y2.to(self.cd) * scale2
         x.add_((v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps) * post_weight.to(self.cd)).to(x.dtype))
         if out is not None:
             u = x.to(self.cd)

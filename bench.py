@@ -652,7 +652,7 @@ class DesignTimer(KernelClassTimer):
                                           "attention_talk", "residual_norm_update", "add_rows", "scaled_sum", "token_side_gate",
                                           "softcap", "token_shift_mix", "linear_scan", "gated_unit_scan", "rotary_store",
                                           "rotate_rows", "paged_attention_streams", "moe_route", "moe_plan", "moe_linear",
-                                          "moe_combine")
+                                          "moe_combine", "moe_plan_padded", "moe_gather", "moe_linear_grouped")
 
     def __init__(self, kernels, vocab, pairs, key_bytes):
         super().__init__(kernels, vocab)
@@ -686,6 +686,10 @@ class DesignTimer(KernelClassTimer):
             x, w, out = a[0], a[1], a[5]
             experts = min(w.shape[0], out.shape[0])           # experts whose matrices a step has to read at the least
             cls, tf, by = "experts", 2 * out.shape[0] * w.shape[1] * w.shape[2], experts * w.shape[1] * w.shape[2] * w.element_size()
+        elif name == "moe_linear_grouped":
+            w, tiles, out = a[1], a[2], a[3]
+            pairs = out.shape[0] - w.shape[0] * 127          # the rows of the padded list that are pairs, at the least
+            cls, tf, by = "experts", 2 * max(pairs, 0) * w.shape[1] * w.shape[2], w.numel() * w.element_size()
         elif name in ("linear", "linear_residual_norm"):
             x, w = a[0], a[1]
             cls = "lm_head" if w.shape[0] == self.vocab else "products"

@@ -169,6 +169,11 @@ struct TcFold {
   const int* qk_slots;        // [n_rows] page * page_size + offset, negative: store nothing (null: no store)
   bf16* qk_pages;             // [page][k | v][kv head][offset][128]
   int qk_page_size;
+  // The grouped product of routed experts (one tile of 128 rows per CTA, no cluster): w holds the experts' matrices one
+  // after the other, grp_w_rows rows each; the rows of x are sorted by expert in segments padded to 128, and tile t of rows
+  // belongs to expert grp_tile_expert[t] (negative: the tile is unused and its CTAs return at once).
+  const int* grp_tile_expert; // null: off
+  int grp_w_rows;
 };
 __device__ __forceinline__ float tc_row_factor(const TcFold& f, int row, int n_rows) {
   if (!f.rs_partials || row >= n_rows) return 1.f;
@@ -223,6 +228,13 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;     // warp-uniform
   const int m0 = blockIdx.y * (MH * G_BM), n0 = blockIdx.x * FO;
+  int w0 = n0;                                                    // first row of this tile's w rows
+  if (fold.grp_tile_expert) {
+    ifb_pdl_wait();                                               // the list of tiles is the predecessor's
+    const int e = fold.grp_tile_expert[blockIdx.y];
+    if (e < 0) { ifb_pdl_trigger(); return; }                     // an unused tile: before any barrier or tensor memory exists
+    w0 = e * fold.grp_w_rows + n0;
+  }
   // With splits > 1 (plain epilogue, one 128-row tile per CTA) the CTAs of a tile are a cluster along z: CTA z
   // multiplies the z-th part of the k range, leaves its float32 tile in its shared memory, and after a cluster barrier
   // adds, in the order of z, a slice of the tile's rows over all CTAs' copies and stores it.
@@ -254,8 +266,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       for (int kb = 0; kb < first; ++kb) {
         unsigned char* stage = smem + kb * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full[kb], Cfg::STAGE_BYTES);
-        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[kb], (kb0 + kb) * G_BK, n0);       // FO rows of w
-        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[kb], (kb0 + kb) * G_BK, o_out + n0);
+        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[kb], (kb0 + kb) * G_BK, w0);       // FO rows of w
+        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[kb], (kb0 + kb) * G_BK, o_out + w0);
       }
     }
     __syncwarp();
@@ -274,8 +286,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
         unsigned char* stage = smem + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
         tma_load_2d(stage, &tmap_x, &full[s], (kb0 + kb) * G_BK, m0);
-        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[s], (kb0 + kb) * G_BK, n0);
-        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[s], (kb0 + kb) * G_BK, o_out + n0);
+        tma_load_2d(stage + Cfg::A_BYTES, &tmap_w, &full[s], (kb0 + kb) * G_BK, w0);
+        if (EPI) tma_load_2d(stage + Cfg::A_BYTES + Cfg::B_BYTES / 2, &tmap_w, &full[s], (kb0 + kb) * G_BK, o_out + w0);
       }
       __syncwarp();
     }
@@ -774,11 +786,12 @@ static int tc_launch_persistent(const void* x, const void* w, void* out, int n, 
 
 template <typename Cfg, typename TO>
 static int tc_launch_cfg(const void* x, const void* w, void* out, int n, int o, int k, int* err, cudaStream_t s, const TcFold& fold,
-                         int splits = 1) {
+                         int splits = 1, long long w_rows = 0) {
   CUtensorMap mx, mw;
   int st = make_map(&mx, x, n, k, Cfg::MH * G_BM);
   if (st) return st;
-  st = make_map(&mw, w, Cfg::EPI ? 2 * o : o, k, Cfg::EPI ? Cfg::NACC / 2 : Cfg::NACC);
+  if (w_rows > 0x7fffffffLL) return IFB_ERR_SIZE;
+  st = make_map(&mw, w, w_rows ? (int)w_rows : (Cfg::EPI ? 2 * o : o), k, Cfg::EPI ? Cfg::NACC / 2 : Cfg::NACC);
   if (st) return st;
   IFB_ALLOW_SMEM((linear_tcgen05_kernel<Cfg, TO>), Cfg::SMEM_BYTES);
   dim3 grid((o + Cfg::FO - 1) / Cfg::FO, (n + Cfg::MH * G_BM - 1) / (Cfg::MH * G_BM), splits);
@@ -889,6 +902,31 @@ IFB_EXPORT int ifb_linear_tcgen05_ex(const void* x, const void* w, void* out, in
   if (out_dtype == IFB_F32)
     return epilogue ? tc_launch<1, float>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream)
                     : tc_launch<0, float>(x, w, out, n_rows, out_features, k_dim, err, shape, splits, fold, stream);
+  return IFB_ERR_DTYPE;
+}
+
+// The grouped product of routed experts.  x [rows, k]: the rows sorted by expert in segments padded to 128 (rows a multiple
+// of 128); w [experts][out_features (x2 with the silu_gate epilogue)][k]; tile_expert [rows / 128]: the expert of each tile of
+// rows, negative for unused tiles (device memory, written by a kernel before this one in the stream); out [rows, out_features].
+IFB_EXPORT int ifb_linear_tcgen05_grouped(const void* x, const void* w, void* out, int out_dtype, int rows, int experts,
+                                          int out_features, int k_dim, int epilogue, const int* tile_expert, int* err,
+                                          cudaStream_t stream) {
+  if (rows <= 0 || out_features <= 0) return IFB_OK;
+  if (k_dim < 8 || k_dim % 8 || rows % G_BM || experts < 1) return IFB_ERR_SIZE;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return IFB_ERR_ALIGN;
+  if ((epilogue != 0 && epilogue != 1) || !tile_expert) return IFB_ERR_ARG;
+  TcFold fold = {};
+  fold.grp_tile_expert = tile_expert;
+  fold.grp_w_rows = (epilogue ? 2 : 1) * out_features;
+  const long long w_rows = (long long)experts * fold.grp_w_rows;
+  using Plain = GemmCfg<0, 1, 128, 3>;
+  using Gated = GemmCfg<1, 1, 256, 2>;
+  if (out_dtype == IFB_BF16)
+    return epilogue ? tc_launch_cfg<Gated, bf16>(x, w, out, rows, out_features, k_dim, err, stream, fold, 1, w_rows)
+                    : tc_launch_cfg<Plain, bf16>(x, w, out, rows, out_features, k_dim, err, stream, fold, 1, w_rows);
+  if (out_dtype == IFB_F32)
+    return epilogue ? tc_launch_cfg<Gated, float>(x, w, out, rows, out_features, k_dim, err, stream, fold, 1, w_rows)
+                    : tc_launch_cfg<Plain, float>(x, w, out, rows, out_features, k_dim, err, stream, fold, 1, w_rows);
   return IFB_ERR_DTYPE;
 }
 

@@ -113,6 +113,94 @@ IFB_EXPORT int ifb_moe_plan(const int* ids, int pairs, int experts, int* offsets
 }
 
 // ------------------------------------------------------------------------------------------
+// The pair list with every expert's segment padded to a multiple of `pad` places (the row tile of the tcgen05 grouped
+// product, which needs an expert's rows contiguous and tiles that do not straddle experts): offsets[e] is the segment's
+// padded start, perm[place] = -1 in the padding, tile_expert[t] the expert of tile t of `pad` places, -1 for the tiles
+// after the last segment (tiles_total of them exist).  A block per expert; each counts all experts' pairs itself.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(MP_THREADS)
+moe_plan_padded_kernel(const int* __restrict__ ids, int pairs, int experts, int pad, int* __restrict__ offsets,
+                       int* __restrict__ perm, int* __restrict__ pos, int* __restrict__ tile_expert, int tiles_total) {
+  __shared__ int hist[256];
+  __shared__ int warp_tot[MP_THREADS / 32];
+  __shared__ int seg[3];                 // start, count, padded count of this block's expert
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 256; i += MP_THREADS) hist[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += MP_THREADS) { const int id = ids[i]; if (id >= 0 && id < experts) atomicAdd(&hist[id], 1); }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int start = 0;
+    for (int j = 0; j < e; ++j) start += (hist[j] + pad - 1) / pad * pad;
+    seg[0] = start; seg[1] = hist[e]; seg[2] = (hist[e] + pad - 1) / pad * pad;
+    offsets[e] = start;
+    if (e == experts - 1) offsets[experts] = start + seg[2];
+  }
+  __syncthreads();
+  const int start = seg[0], count = seg[1], padded = seg[2];
+  for (int i = start + count + threadIdx.x; i < start + padded; i += MP_THREADS) perm[i] = -1;
+  for (int t = start / pad + threadIdx.x; t < (start + padded) / pad; t += MP_THREADS) tile_expert[t] = e;
+  if (e == experts - 1)
+    for (int t = (start + padded) / pad + threadIdx.x; t < tiles_total; t += MP_THREADS) tile_expert[t] = -1;
+  int base = start;
+  for (int i0 = 0; i0 < pairs; i0 += MP_THREADS) {
+    const int i = i0 + threadIdx.x;
+    const bool hit = i < pairs && ids[i] == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+    __syncthreads();
+    if (lane == 0) warp_tot[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < MP_THREADS / 32; ++w) { const int c = warp_tot[w]; if (w < warp) before += c; total += c; }
+    if (hit) {
+      const int place = base + before + __popc(ballot & ((1u << lane) - 1u));
+      perm[place] = i;
+      pos[i] = place;
+    }
+    base += total;
+  }
+}
+
+IFB_EXPORT int ifb_moe_plan_padded(const int* ids, int pairs, int experts, int pad, int* offsets, int* perm, int* pos,
+                                   int* tile_expert, int tiles_total, cudaStream_t stream) {
+  if (experts < 1 || experts > 256 || pad < 1) return IFB_ERR_SIZE;
+  if (pairs < 0 || (long long)tiles_total * pad < (long long)pairs + (long long)experts * (pad - 1)) return IFB_ERR_ARG;
+  return ifb_launch(moe_plan_padded_kernel, dim3(experts), dim3(MP_THREADS), 0, stream, ids, pairs, experts, pad, offsets, perm, pos,
+                    tile_expert, tiles_total);
+}
+
+// out[place][:] = x[perm[place] / top][:], zeros where perm[place] < 0; places of unused tiles are left alone.
+// bfloat16 rows of k elements, k a multiple of 8; a block per place.
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ perm, int top, const int* __restrict__ tile_expert,
+                       int pad, uint4* __restrict__ out, int k8) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int place = blockIdx.x;
+  if (tile_expert[place / pad] < 0) return;
+  const int p = perm[place];
+  uint4* dst = out + (size_t)place * k8;
+  if (p < 0) {
+    for (int i = threadIdx.x; i < k8; i += blockDim.x) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const uint4* src = x + (size_t)(p / top) * k8;
+  for (int i = threadIdx.x; i < k8; i += blockDim.x) dst[i] = src[i];
+}
+
+IFB_EXPORT int ifb_moe_gather_rows(const void* x, const int* perm, int top, const int* tile_expert, int pad, void* out, int places,
+                                   int k, cudaStream_t stream) {
+  if (places <= 0) return IFB_OK;
+  if (k < 8 || k % 8 || top < 1 || pad < 1) return IFB_ERR_SIZE;
+  if (((uintptr_t)x & 15) || ((uintptr_t)out & 15)) return IFB_ERR_ALIGN;
+  return ifb_launch(moe_gather_rows_kernel, dim3(places), dim3(128), 0, stream, (const uint4*)x, perm, top, tile_expert, pad,
+                    (uint4*)out, k / 8);
+}
+
+// ------------------------------------------------------------------------------------------
 // The grouped product.  Row i of `out` belongs to the expert e with offsets[e] <= i < offsets[e + 1] and is
 //     x[src(i)] w[e]^T,   src(i) = perm[i] / top (perm null: i),   w [experts][o_w][k]
 // GATED: w[e] holds o gate rows and then o up rows, and out[i][j] = silu(gate_j) * up_j.  A block is a tile of ML_ROWS

@@ -116,6 +116,8 @@ class CudaKernels:
         self._gu_scratch = None
         self.gated_unit_chunked_calls = 0
         self.moe_tensor_cores = os.environ.get("INFURNACE_MOE_MMA", "1") != "0"
+        self.moe_tcgen05 = os.environ.get("INFURNACE_MOE_TCGEN05", "1") != "0"     # prompts' expert products on tcgen05
+        self.moe_tcgen05_calls = 0
         self.linear_scan_blocked_calls = 0
         self.stream_attention_calls = 0
         self._mix = None               # the library of post-norm sublayers, the gated recurrence and talking attention
@@ -883,6 +885,8 @@ class CudaKernels:
             m.ifb_moe_linear.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                          c_int, c_int, c_int, c_int, c_int, c_void_p]
             m.ifb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+            m.ifb_moe_plan_padded.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+            m.ifb_moe_gather_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         return self._hyb
 
     def residual_norm_update(self, x, y, post_weight, eps, out=None, next_weight=None, y2=None, scale=1.0, scale2=1.0):
@@ -1159,12 +1163,75 @@ class CudaKernels:
                                               int(top), out.data_ptr(), _code(out), rows, experts, o, k, 1 if gated else 0,
                                               1 if self.moe_tensor_cores else 0, self._stream()), "moe_linear")
 
+    # The experts' products of a prompt on the tcgen05 kernel: every expert's rows contiguous in segments padded to the
+    # kernel's tile of 128 rows (TMA reads whole tiles; a tile has one expert).
+    MOE_TILE = 128
+
+    def moe_grouped_tc_ok(self, pairs, dtype, *weights):
+        """Whether a step of ``pairs`` (token, choice) pairs runs its experts' products on the tcgen05 kernel: bfloat16,
+        more pairs than the few-rows form takes, every k a multiple of 8."""
+        return (self.moe_tcgen05 and dtype == torch.bfloat16 and pairs > 256
+                and all(w.dtype == torch.bfloat16 and w.shape[2] % 8 == 0 and w.shape[1] % 8 == 0 for w in weights))
+
+    def moe_padded_rows(self, pairs, num_experts):
+        """Places of the padded pair list: the most that ``pairs`` pairs over the experts can need, a multiple of the tile."""
+        t = self.MOE_TILE
+        return -(-(pairs + num_experts * (t - 1)) // t) * t
+
+    def moe_plan_padded(self, ids, num_experts, offsets, perm, pos, tile_expert):
+        """As :meth:`moe_plan` with every expert's segment padded to the tile: perm [moe_padded_rows] (-1 in the padding),
+        pos [pairs] (pair -> padded place), tile_expert [places / tile] (-1: unused tile)."""
+        _dense(ids, "ids", torch.int32), _dense(offsets, "offsets", torch.int32), _dense(perm, "perm", torch.int32)
+        _dense(pos, "pos", torch.int32), _dense(tile_expert, "tile_expert", torch.int32)
+        pairs = ids.numel()
+        if offsets.numel() != num_experts + 1 or pos.numel() != pairs or perm.numel() != tile_expert.numel() * self.MOE_TILE \
+                or perm.numel() < pairs + num_experts * (self.MOE_TILE - 1):
+            raise KernelError("moe_plan_padded: sizes of offsets, perm, pos and tile_expert do not match")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_moe_plan_padded(ids.data_ptr(), pairs, int(num_experts), self.MOE_TILE, offsets.data_ptr(),
+                                                   perm.data_ptr(), pos.data_ptr(), tile_expert.data_ptr(), tile_expert.numel(),
+                                                   self._stream()), "moe_plan_padded")
+
+    def moe_gather(self, x, perm, top, tile_expert, out):
+        """out[place] = x[perm[place] // top], zeros in the padding; the rows of unused tiles are left alone."""
+        _dense(x, "x", torch.bfloat16), _dense(perm, "perm", torch.int32), _dense(tile_expert, "tile_expert", torch.int32)
+        _dense(out, "out", torch.bfloat16)
+        if out.shape != (perm.numel(), x.shape[1]) or perm.numel() != tile_expert.numel() * self.MOE_TILE:
+            raise KernelError("moe_gather: out has a row for every place of perm")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_moe_gather_rows(x.data_ptr(), perm.data_ptr(), int(top), tile_expert.data_ptr(), self.MOE_TILE,
+                                                   out.data_ptr(), perm.numel(), x.shape[1], self._stream()), "moe_gather")
+
+    def moe_linear_grouped(self, x, w, tile_expert, out, epilogue="none"):
+        """out[place] = x[place] @ w[tile_expert[place // tile]]^T on the tcgen05 kernel (csrc/linear_tcgen05.cu, its grouped
+        mode); x [places, k] sorted by expert in padded segments, w [experts, o (2 o with "silu_gate"), k]."""
+        _dense(x, "x", torch.bfloat16), _dense(w, "w", torch.bfloat16), _dense(tile_expert, "tile_expert", torch.int32), _dense(out, "out")
+        gated = epilogue == "silu_gate"
+        if epilogue not in ("none", "silu_gate"):
+            raise KernelError(f"moe_linear_grouped: epilogue {epilogue!r}; known: none, silu_gate")
+        rows, o = out.shape
+        experts, ow, k = w.shape
+        if x.shape != (rows, k) or ow != (2 * o if gated else o) or rows != tile_expert.numel() * self.MOE_TILE:
+            raise KernelError("moe_linear_grouped: sizes of x, w, tile_expert and out do not match")
+        lib = self._tc_lib()
+        if not getattr(lib, "_grouped_declared", False):
+            lib.ifb_linear_tcgen05_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                       c_void_p, c_void_p, c_void_p]
+            lib._grouped_declared = True
+        self.launches += 1
+        self.moe_tcgen05_calls += 1
+        self._err_armed = True
+        _check(lib.ifb_linear_tcgen05_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), rows, experts, o, k,
+                                              1 if gated else 0, tile_expert.data_ptr(), self._dev_err.data_ptr(), self._stream()),
+               "moe_linear_grouped")
+
     def moe_combine(self, y, pos, gates, out):
-        """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending, float32."""
+        """out[n] = sum_j gates[n, j] * y[pos[n * top + j]], j ascending, float32 (y may hold more rows than pairs: a
+        padded list)."""
         _dense(y, "y", torch.float32), _dense(pos, "pos", torch.int32), _dense(gates, "gates", torch.float32)
         _dense(out, "out", torch.float32)
         n, top = gates.shape
-        if pos.numel() != n * top or y.shape != (n * top, out.shape[1]) or out.shape[0] != n:
+        if pos.numel() != n * top or y.shape[0] < n * top or y.shape[1] != out.shape[1] or out.shape[0] != n:
             raise KernelError("moe_combine: sizes of y, pos, gates and out do not match")
         self.launches += 1
         _check(self._hyb_lib().ifb_moe_combine(y.data_ptr(), pos.data_ptr(), gates.data_ptr(), out.data_ptr(), n, top,

@@ -15,7 +15,10 @@ class RoutedExperts:
     the softmax over them; one lists, per expert, the (token, choice) pairs that chose it, in token order (all on the
     device: the step's launches depend on its sizes only).  The experts' products then run as two grouped launches
     over that list (gate | up with the activation in the epilogue, then down) against the experts' matrices stacked
-    along a leading axis, and one kernel sums each token's results in the order of its choices, in float32."""
+    along a leading axis, and one kernel sums each token's results in the order of its choices, in float32.  bfloat16
+    steps of more than 256 pairs (prompts) take the tcgen05 kernel in its grouped mode, over a list whose segments are
+    padded to that kernel's tile of 128 rows (``_forward_padded``); fewer pairs, float32 and odd sizes the kernels of
+    csrc/moe.cu."""
 
     graph_safe = True
 
@@ -39,6 +42,9 @@ class RoutedExperts:
         gates = ctx.buffer("moe_gates", (n, s.top), torch.float32)
         k.moe_route(logits, s.top, ids, gates)
         pairs = n * s.top
+        ok = getattr(k, "moe_grouped_tc_ok", None)
+        if ok is not None and ok(pairs, h.dtype, self.w_gate_up, self.w_down):
+            return self._forward_padded(h, ctx, ids, gates)
         offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32, rows=E + 1)
         perm = ctx.buffer("moe_perm", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
         pos = ctx.buffer("moe_pos", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
@@ -47,6 +53,29 @@ class RoutedExperts:
         k.moe_linear(h, self.w_gate_up, offsets, perm, s.top, act, epilogue="silu_gate")
         y = ctx.buffer("moe_y", (pairs, s.hidden_size), torch.float32, rows=ctx.max_rows * s.top)
         k.moe_linear(act, self.w_down, offsets, None, 1, y)
+        delta = ctx.buffer("delta_ffn", (n, s.hidden_size), torch.float32)
+        k.moe_combine(y, pos, gates, delta)
+        return delta
+
+    def _forward_padded(self, h, ctx, ids, gates):
+        """A prompt's experts on the tcgen05 kernel: the pair list with every expert's segment padded to the kernel's row
+        tile, the tokens' rows gathered into that order, the two products as grouped launches whose row tiles each belong to
+        one expert, the weighted sum through the padded places."""
+        s, k, E = self.spec, self.k, self.num_experts
+        n = h.shape[0]
+        pairs = n * s.top
+        places, cap = k.moe_padded_rows(pairs, E), k.moe_padded_rows(ctx.max_rows * s.top, E)
+        offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32, rows=E + 1)
+        perm = ctx.buffer("moe_perm_padded", (places,), torch.int32, rows=cap)
+        pos = ctx.buffer("moe_pos", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
+        tiles = ctx.buffer("moe_tiles", (places // k.MOE_TILE,), torch.int32, rows=cap // k.MOE_TILE)
+        k.moe_plan_padded(ids, E, offsets, perm, pos, tiles)
+        xs = ctx.buffer("moe_xs", (places, h.shape[1]), self.rt.act_dtype, rows=cap)
+        k.moe_gather(h, perm, s.top, tiles, xs)
+        act = ctx.buffer("moe_act_padded", (places, s.intermediate_size), self.rt.act_dtype, rows=cap)
+        k.moe_linear_grouped(xs, self.w_gate_up, tiles, act, epilogue="silu_gate")
+        y = ctx.buffer("moe_y_padded", (places, s.hidden_size), torch.float32, rows=cap)
+        k.moe_linear_grouped(act, self.w_down, tiles, y)
         delta = ctx.buffer("delta_ffn", (n, s.hidden_size), torch.float32)
         k.moe_combine(y, pos, gates, delta)
         return delta

@@ -280,7 +280,9 @@ def _attention_case(K, H, G, d, dv, rot, inter, ps, dtype, lens_new, lens_old, w
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,rot,inter,ps", [(4, 2, 16, 8, 8, False, 16), (6, 6, 8, 16, 8, False, 8), (8, 1, 128, 128, 32, False, 16),
                                                     (3, 1, 24, 40, 12, True, 4), (2, 2, 64, 64, 0, False, 32), (5, 5, 256, 2, 256, False, 16),
-                                                    (6, 2, 32, 32, 2, False, 16), (2, 2, 48, 48, 48, False, 16), (4, 4, 16, 16, 8, True, 16)])
+                                                    (6, 2, 32, 32, 2, False, 16), (2, 2, 48, 48, 48, False, 16), (4, 4, 16, 16, 8, True, 16),
+                                                    (4, 2, 80, 80, 40, False, 16), (2, 1, 96, 96, 96, False, 8), (2, 2, 256, 256, 64, False, 16),
+                                                    (32, 1, 64, 64, 32, False, 16)])
 def test_rotated_values_attention_kernels(K, H, G, d, dv, rot, inter, ps, dtype):
     _attention_case(K, H, G, d, dv, rot, inter, ps, dtype, [33, 1, 2, 1], [0, 70, 15, 16])
     _attention_case(K, H, G, d, dv, rot, inter, ps, dtype, [5, 1], [40, 40], window=7, seed=1)
@@ -328,6 +330,27 @@ def _moe_case(K, n, E, top, k, o, dtype, seed):
     REF.moe_combine(y_ref.float(), pos_ref, gates_ref.float(), out_ref)
     K.moe_combine(y, pos, gates, out)
     close(out, out_ref, tol * 2, "sum")
+    if dtype == torch.bfloat16 and k % 8 == 0 and o % 8 == 0:
+        # the padded list and the tcgen05 grouped products (the route of prompts), forced here whatever the number of pairs
+        places = K.moe_padded_rows(P_, E)
+        perm2, pos2 = torch.full((places,), -7, device="cuda", dtype=torch.int32), torch.zeros(P_, device="cuda", dtype=torch.int32)
+        tiles = torch.full((places // K.MOE_TILE,), -7, device="cuda", dtype=torch.int32)
+        K.moe_plan_padded(ids, E, off, perm2, pos2, tiles)
+        starts, t_host = off.cpu().tolist(), tiles.cpu().tolist()
+        counts = torch.bincount(ids_ref.reshape(-1).long(), minlength=E).tolist()
+        assert all(a % K.MOE_TILE == 0 for a in starts) and starts[-1] == sum(-(-c // K.MOE_TILE) * K.MOE_TILE for c in counts)
+        assert t_host == [e for e in range(E) for _ in range(-(-counts[e] // K.MOE_TILE))] + [-1] * (len(t_host) - starts[-1] // K.MOE_TILE)
+        assert sorted(pos2.cpu().tolist()) == sorted(i for e in range(E) for i in range(starts[e], starts[e] + counts[e]))
+        xs = torch.full((places, k), float("nan"), device="cuda", dtype=dtype)
+        K.moe_gather(x.cuda(), perm2, top, tiles, xs)
+        act2 = torch.full((places, o), float("nan"), device="cuda", dtype=dtype)
+        K.moe_linear_grouped(xs, w1.cuda(), tiles, act2, epilogue="silu_gate")
+        y2 = torch.full((places, k), float("nan"), device="cuda")
+        K.moe_linear_grouped(act2, w2.cuda(), tiles, y2)
+        out2 = torch.zeros(n, k, device="cuda")
+        K.moe_combine(y2, pos2, gates, out2)
+        K.check_device_errors()
+        close(out2, out_ref, tol * 2, "sum through the padded list")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -12,13 +12,8 @@
 // (up to MR_PER_LANE * 32 experts); lane j keeps the j-th chosen logit (up to 32 choices).
 // ------------------------------------------------------------------------------------------
 constexpr int MR_PER_LANE = 8;
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ gates, int rows, int experts,
-                 int top) {
-  ifb_pdl_wait();
-  ifb_pdl_trigger();
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= rows) return;
+__device__ __forceinline__ void mr_route_row(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ gates,
+                                             int row, int experts, int top, int lane) {
   float val[MR_PER_LANE];
 #pragma unroll
   for (int j = 0; j < MR_PER_LANE; ++j) {
@@ -50,6 +45,51 @@ moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float*
   const float p = lane < top ? expf(mine - first) : 0.f;
   sum = warp_sum(p);
   if (lane < top) gates[(size_t)row * top + lane] = p / sum;
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ gates, int rows, int experts,
+                 int top) {
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  mr_route_row(logits, ids, gates, row, experts, top, lane);
+}
+
+// The router and the pair list of a step of few rows (decode) in one launch: one block routes the rows, a warp each in
+// turn, then a thread per expert counts its pairs, finds its offset and lists them in ascending pair number.
+constexpr int MS_THREADS = 256;
+__global__ void __launch_bounds__(MS_THREADS)
+moe_route_plan_small_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ gates, int rows, int experts,
+                            int top, int* __restrict__ offsets, int* __restrict__ perm, int* __restrict__ pos) {
+  __shared__ int cnt[MS_THREADS];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = warp; row < rows; row += MS_THREADS / 32) mr_route_row(logits, ids, gates, row, experts, top, lane);
+  __syncthreads();                                 // the block's own writes of ids are visible to it
+  const int e = threadIdx.x, pairs = rows * top;
+  int mine = 0;
+  if (e < experts)
+    for (int i = 0; i < pairs; ++i) mine += ids[i] == e ? 1 : 0;
+  cnt[threadIdx.x] = mine;
+  __syncthreads();
+  if (e >= experts) return;
+  int place = 0;
+  for (int j = 0; j < e; ++j) place += cnt[j];
+  offsets[e] = place;
+  if (e == experts - 1) offsets[experts] = place + mine;
+  for (int i = 0; i < pairs && mine > 0; ++i)
+    if (ids[i] == e) { perm[place] = i; pos[i] = place; ++place; }
+}
+
+IFB_EXPORT int ifb_moe_route_plan_small(const float* logits, int* ids, float* gates, int rows, int experts, int top, int* offsets,
+                                        int* perm, int* pos, cudaStream_t stream) {
+  if (rows <= 0) return IFB_OK;
+  if (experts < 1 || experts > MS_THREADS || top < 1 || top > experts || top > 32 || (long long)rows * top > 4096) return IFB_ERR_SIZE;
+  return ifb_launch(moe_route_plan_small_kernel, dim3(1), dim3(MS_THREADS), 0, stream, logits, ids, gates, rows, experts, top,
+                    offsets, perm, pos);
 }
 
 IFB_EXPORT int ifb_moe_route(const float* logits, int* ids, float* gates, int rows, int experts, int top, cudaStream_t stream) {

@@ -885,6 +885,8 @@ class CudaKernels:
             m.ifb_moe_linear.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                                          c_int, c_int, c_int, c_int, c_int, c_void_p]
             m.ifb_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+            m.ifb_moe_route_plan_small.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p]
             m.ifb_moe_plan_padded.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
             m.ifb_moe_gather_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         return self._hyb
@@ -1128,6 +1130,24 @@ class CudaKernels:
         self.launches += 1
         _check(self._hyb_lib().ifb_moe_route(logits.data_ptr(), ids.data_ptr(), gates.data_ptr(), n, experts, int(top),
                                              self._stream()), "moe_route")
+
+    MOE_SMALL_PAIRS = 512      # up to here the router and the pair list are one launch of one block
+
+    def moe_route_plan(self, logits, top, ids, gates, offsets, perm, pos):
+        """:meth:`moe_route` and :meth:`moe_plan` of a step; one launch where the step has few pairs (decode)."""
+        n, experts = logits.shape
+        if n * top > self.MOE_SMALL_PAIRS or experts > 256:
+            self.moe_route(logits, top, ids, gates)
+            return self.moe_plan(ids, experts, offsets, perm, pos)
+        _dense(logits, "logits", torch.float32), _dense(ids, "ids", torch.int32), _dense(gates, "gates", torch.float32)
+        _dense(offsets, "offsets", torch.int32), _dense(perm, "perm", torch.int32), _dense(pos, "pos", torch.int32)
+        if ids.shape != (n, top) or gates.shape != (n, top) or offsets.numel() != experts + 1 or perm.numel() != n * top \
+                or pos.numel() != n * top:
+            raise KernelError("moe_route_plan: sizes of ids, gates, offsets, perm and pos do not match")
+        self.launches += 1
+        _check(self._hyb_lib().ifb_moe_route_plan_small(logits.data_ptr(), ids.data_ptr(), gates.data_ptr(), n, experts, int(top),
+                                                        offsets.data_ptr(), perm.data_ptr(), pos.data_ptr(), self._stream()),
+               "moe_route_plan")
 
     def moe_plan(self, ids, num_experts, offsets, perm, pos):
         """The (row, choice) pairs listed by expert in ascending pair number: offsets [experts + 1], perm [pairs]

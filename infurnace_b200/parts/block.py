@@ -148,11 +148,23 @@ class TokenSide:
 register_part(TokenSideSpec, TokenSide)
 
 
+class ReadyInput:
+    """What a sandwich block hands to the sandwich block after it instead of a pending delta: x is up to date, and
+    ``values`` already holds the next block's first pre-norm of it (written by this block's last stream update)."""
+    __slots__ = ("values",)
+
+    def __init__(self, values):
+        self.values = values
+
+
 class SandwichBlock:
     """x += post1(mixer(pre1(x))); x += post2(ffn(pre2(x))); then the token side input.  Every update of the stream
     is one kernel that normalises the sublayer's float32 result, adds it to x in float32 and, in the same pass, writes
-    what the next product reads: the next pre-norm of x, or x itself in the products' dtype.  x is up to date when the
+    what the next product reads: the next pre-norm of x (the next BLOCK's first norm too, when a block of this kind
+    follows directly: it gets a :class:`ReadyInput`), or x itself in the products' dtype.  x is up to date when the
     block returns; it hands on no pending delta."""
+
+    hands_over_input = True          # the decoder passes ``next_layer`` when the next layer call is a block of this kind
 
     def __init__(self, spec: SandwichBlockSpec, weights, runtime):
         self.spec = spec
@@ -184,26 +196,31 @@ class SandwichBlock:
             self.k.residual_norm_update(x, y, post.weight, post.spec.eps, out=out, next_weight=nxt)
         return out
 
-    def forward(self, x, pending, ctx, call):
-        if pending is not None:                      # a block of another kind ran before and left its last delta
-            if isinstance(pending, Folded):
-                raise TypeError("a sandwich block cannot take a folded norm from the block before it")
-            x.add_(pending)
-        h = ctx.buffer("h", x.shape, self.rt.act_dtype)
-        self.mixer_norm.forward(x, h)
+    def forward(self, x, pending, ctx, call, next_layer=None):
+        if isinstance(pending, ReadyInput):          # the block before this one wrote our first norm already
+            h = pending.values
+        else:
+            if pending is not None:                  # a block of another kind ran before and left its last delta
+                if isinstance(pending, Folded):
+                    raise TypeError("a sandwich block cannot take a folded norm from the block before it")
+                x.add_(pending)
+            h = ctx.buffer("h", x.shape, self.rt.act_dtype)
+            self.mixer_norm.forward(x, h)
+        ahead = next_layer.mixer_norm if isinstance(next_layer, SandwichBlock) else None
         if getattr(self.mixer, "can_return_weighted", False):
             y = self.mixer.forward(h, ctx, call, weighted=True)
         else:
             y = self.mixer.forward(h, ctx, call)
+        last_norm = None if self.side is not None else ahead        # the block's last update also writes the next block's norm
         if self.ffn is not None:
             h = self._update(x, y, self.mixer_post, ctx, then_norm=self.ffn_norm)
             y = self.ffn.forward(h, ctx)
-            xa = self._update(x, y, self.ffn_post, ctx, then_copy=self.side is not None)
+            xa = self._update(x, y, self.ffn_post, ctx, then_norm=last_norm, then_copy=self.side is not None)
         else:
-            xa = self._update(x, y, self.mixer_post, ctx, then_copy=self.side is not None)
+            xa = self._update(x, y, self.mixer_post, ctx, then_norm=last_norm, then_copy=self.side is not None)
         if self.side is not None:
-            self._update(x, self.side.forward(xa, ctx), self.side.norm, ctx)
-        return None
+            xa = self._update(x, self.side.forward(xa, ctx), self.side.norm, ctx, then_norm=ahead)
+        return ReadyInput(xa) if ahead is not None else None
 
 
 register_part(SandwichBlockSpec, SandwichBlock)

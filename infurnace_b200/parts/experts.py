@@ -40,15 +40,15 @@ class RoutedExperts:
         k.linear(h, self.router, logits)
         ids = ctx.buffer("moe_ids", (n, s.top), torch.int32)
         gates = ctx.buffer("moe_gates", (n, s.top), torch.float32)
-        k.moe_route(logits, s.top, ids, gates)
         pairs = n * s.top
         ok = getattr(k, "moe_grouped_tc_ok", None)
         if ok is not None and ok(pairs, h.dtype, self.w_gate_up, self.w_down):
+            k.moe_route(logits, s.top, ids, gates)
             return self._forward_padded(h, ctx, ids, gates)
         offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32, rows=E + 1)
         perm = ctx.buffer("moe_perm", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
         pos = ctx.buffer("moe_pos", (pairs,), torch.int32, rows=ctx.max_rows * s.top)
-        k.moe_plan(ids, E, offsets, perm, pos)
+        k.moe_route_plan(logits, s.top, ids, gates, offsets, perm, pos)        # one launch for a step of few pairs
         act = ctx.buffer("moe_act", (pairs, s.intermediate_size), self.rt.act_dtype, rows=ctx.max_rows * s.top)
         k.moe_linear(h, self.w_gate_up, offsets, perm, s.top, act, epilogue="silu_gate")
         y = ctx.buffer("moe_y", (pairs, s.hidden_size), torch.float32, rows=ctx.max_rows * s.top)

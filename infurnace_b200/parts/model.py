@@ -133,6 +133,8 @@ class DecoderModel:
             nxt = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             if getattr(layer, "folds_norms", False) and getattr(nxt, "folds_norms", False):
                 pending = layer.forward(x, pending, ctx, call, next_layer=nxt)     # may hand over a folded norm
+            elif getattr(layer, "hands_over_input", False) and getattr(nxt, "hands_over_input", False):
+                pending = layer.forward(x, pending, ctx, call, next_layer=nxt)     # may hand over the next block's input
             else:
                 pending = layer.forward(x, pending, ctx, call)
         m = ctx.num_logit_rows

@@ -487,6 +487,11 @@ class ReferenceKernels:
         ids.copy_(idx[:, :top].to(ids.dtype))
         gates.copy_(torch.softmax(val[:, :top], dim=-1).to(gates.dtype))
 
+    def moe_route_plan(self, logits, top, ids, gates, offsets, perm, pos):
+        """moe_route, then moe_plan."""
+        self.moe_route(logits, top, ids, gates)
+        self.moe_plan(ids, logits.shape[1], offsets, perm, pos)
+
     def moe_plan(self, ids, num_experts, offsets, perm, pos):
         """The pairs (token, choice), numbered token * top + choice, listed by expert in ascending pair number:
         offsets[e] .. offsets[e + 1] are expert e's places in ``perm``; pos[pair] is the pair's place."""

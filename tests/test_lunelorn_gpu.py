@@ -121,8 +121,8 @@ def test_small_stream_kernels(K):
         close(got, want, 2e-6 if dt == torch.float32 else 0.03, "token side gate")
     logits = 40 * torch.randn(5, 77, generator=g)
     want, got = logits.clone().double(), logits.cuda()
-    REF.softcap(want, 15.0)
-    K.softcap(got, 15.0)
+    REF.softcap(want, 12.0)
+    K.softcap(got, 12.0)
     close(got, want, 5e-6, "softcap")
 
 
@@ -148,7 +148,7 @@ def test_token_shift_over_steps_and_slots(K, dtype):
         close(got_last, want_last, 0.0, "saved rows")
 
 
-SCAN_SHAPES = [(2, 8, 12), (3, 16, 8), (1, 24, 40), (4, 48, 48), (2, 64, 64), (2, 128, 300), (1, 130, 20), (2, 33, 600)]
+SCAN_SHAPES = [(2, 8, 12), (3, 16, 8), (1, 24, 40), (3, 48, 48), (2, 64, 64), (2, 128, 300), (1, 130, 20), (2, 33, 600)]
 
 
 @pytest.mark.parametrize("heads,dim,vdim", SCAN_SHAPES)
@@ -190,7 +190,7 @@ def test_matrix_state_recurrence(K, heads, dim, vdim, form):
     assert float(state[0].abs().max()) == 0.0          # the padding request's slot
 
 
-@pytest.mark.parametrize("width", [7, 224, 1000])
+@pytest.mark.parametrize("width", [7, 200, 1000])
 def test_gated_unit_kernel(K, width):
     g = gen(width)
     zb, xb = torch.randn(width, generator=g), torch.randn(width, generator=g)
@@ -278,7 +278,7 @@ def _attention_case(K, H, G, d, dv, rot, inter, ps, dtype, lens_new, lens_old, w
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,d,dv,rot,inter,ps", [(4, 2, 16, 8, 8, False, 16), (6, 6, 8, 16, 8, False, 8), (8, 1, 128, 128, 32, False, 16),
+@pytest.mark.parametrize("H,G,d,dv,rot,inter,ps", [(4, 2, 16, 8, 8, False, 16), (6, 6, 8, 16, 8, False, 8), (8, 2, 128, 128, 64, False, 16),
                                                     (3, 1, 24, 40, 12, True, 4), (2, 2, 64, 64, 0, False, 32), (5, 5, 256, 2, 256, False, 16),
                                                     (6, 2, 32, 32, 2, False, 16), (2, 2, 48, 48, 48, False, 16), (4, 4, 16, 16, 8, True, 16),
                                                     (4, 2, 80, 80, 40, False, 16), (2, 1, 96, 96, 96, False, 8), (2, 2, 256, 256, 64, False, 16),
@@ -314,6 +314,11 @@ def _moe_case(K, n, E, top, k, o, dtype, seed):
                       torch.zeros(P_, device="cuda", dtype=torch.int32))
     K.moe_plan(ids, E, off, perm, pos)
     assert torch.equal(off.cpu(), off_ref) and torch.equal(perm.cpu(), perm_ref) and torch.equal(pos.cpu(), pos_ref)
+    ids_b, gates_b = torch.zeros_like(ids), torch.zeros_like(gates)          # router and list in one call (one launch for few pairs)
+    off_b, perm_b, pos_b = torch.zeros_like(off), torch.zeros_like(perm), torch.zeros_like(pos)
+    K.moe_route_plan(logits.cuda(), top, ids_b, gates_b, off_b, perm_b, pos_b)
+    assert torch.equal(ids_b, ids) and torch.equal(gates_b, gates) and torch.equal(off_b, off) and torch.equal(perm_b, perm) \
+        and torch.equal(pos_b, pos)
     x = torch.randn(n, k, generator=g).to(dtype)
     w1 = (torch.randn(E, 2 * o, k, generator=g) / k ** 0.5).to(dtype)
     w2 = (torch.randn(E, k, o, generator=g) / o ** 0.5).to(dtype)
@@ -354,7 +359,7 @@ def _moe_case(K, n, E, top, k, o, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n,E,top,k,o", [(1, 5, 2, 48, 24), (70, 12, 4, 192, 96), (9, 3, 3, 64, 40), (300, 40, 1, 72, 130), (33, 4, 2, 256, 128)])
+@pytest.mark.parametrize("n,E,top,k,o", [(1, 5, 2, 48, 24), (70, 10, 3, 160, 88), (9, 3, 3, 64, 40), (300, 40, 1, 72, 130), (33, 4, 2, 256, 128)])
 def test_routed_experts_kernels(K, n, E, top, k, o, dtype):
     _moe_case(K, n, E, top, k, o, dtype, n + E)
 

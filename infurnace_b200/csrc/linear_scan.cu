@@ -73,16 +73,24 @@ __device__ __forceinline__ bool ls_find_block(const LinearScanArgs& a, int row, 
 
 constexpr int ls_max_threads(int dmax) { return dmax <= 32 ? 512 : dmax <= 64 ? 256 : 128; }
 
-// out = o / rms(o) (* norm_w) (* silu(gate)) for one (token, head), by one warp; o holds the head's vdim sums
+// out = o / rms(o) (* norm_w) (* silu(gate)) for one (token, head), by one warp; the head's vdim sums are o[e], or with
+// `parts` > 1 the sum over p of o[p * part_stride + e] (the rows of a column were split over several threads)
 template <typename T>
-__device__ __forceinline__ void ls_finish(const LinearScanArgs& a, const float* o, int t, int h, int lane) {
+__device__ __forceinline__ void ls_finish(const LinearScanArgs& a, const float* o, int t, int h, int lane, int parts = 1,
+                                          int part_stride = 0) {
   const int vdim = a.vdim;
   float ss = 0.f;
-  for (int e = lane; e < vdim; e += 32) ss += o[e] * o[e];
+  for (int e = lane; e < vdim; e += 32) {
+    float v = o[e];
+    for (int p = 1; p < parts; ++p) v += o[p * part_stride + e];
+    ss += v * v;
+  }
   const float rn = 1.f / sqrtf(warp_sum(ss) / (float)vdim + a.eps);
   T* dst = (T*)a.out + ((size_t)t * a.heads + h) * vdim;
   for (int e = lane; e < vdim; e += 32) {
-    float y = o[e] * rn;
+    float v = o[e];
+    for (int p = 1; p < parts; ++p) v += o[p * part_stride + e];
+    float y = v * rn;
     if (a.norm_w) y *= load_as_f32(a.norm_w, a.p_dtype, (size_t)h * vdim + e);
     if (a.gate) { const float g = a.gate[(size_t)t * a.ldg + h * vdim + e]; y *= g / (1.f + expf(-g)); }
     dst[e] = from_f32<T>(y);
@@ -209,6 +217,135 @@ linear_scan_kernel(LinearScanArgs a) {
     for (int i = threadIdx.x; i < dim; i += blockDim.x) a.dprod[((size_t)blockIdx.y * a.heads + h) * dim + i] = ap[i];
 }
 
+// The same walk with the rows of a state column split over RS = 2 threads, each with DMAX / 2 of them in registers: a head
+// of few columns then has twice the threads for staging its tokens (decay, key, bonus number), half the chain per thread
+// and half the registers; the two partial sums of an output meet in shared memory at the finish.
+template <typename T, int DMAX, int RS, bool OUT, bool BONUS>
+__global__ void __launch_bounds__(ls_max_threads(DMAX), DMAX <= 64 ? 2 : 1)
+linear_scan_split_kernel(LinearScanArgs a) {
+  constexpr int RPT = DMAX / RS;               // rows per thread
+  extern __shared__ float sm[];
+  ifb_pdl_wait();
+  ifb_pdl_trigger();
+  const int cols = blockDim.x / RS;            // threads along the columns
+  const int cid = threadIdx.x % cols, part = threadIdx.x / cols, r0 = part * RPT;
+  const int h = blockIdx.x / a.slabs, c0 = (blockIdx.x % a.slabs) * cols, c = c0 + cid;
+  const int dim = a.dim, vdim = a.vdim;
+  const int width = min(cols, vdim - c0);      // columns of this block
+  int r = blockIdx.y, t0, t1;
+  if (a.mode == 0) {
+    if (a.seq_lens[r] <= 0) return;
+    t0 = a.cu_q[r]; t1 = a.cu_q[r + 1];
+  } else if (!ls_find_block(a, blockIdx.y, r, t0, t1)) {
+    return;
+  }
+  float* qs = sm;                              // [GROUP][DMAX]
+  float* ks = qs + LS_GROUP * DMAX;            // [GROUP][DMAX]
+  float* ds = ks + LS_GROUP * DMAX;            // [GROUP][DMAX]
+  float* vs = ds + LS_GROUP * DMAX;            // [GROUP][cols]
+  float* os = vs + LS_GROUP * cols;            // [RS][GROUP][cols]
+  float* ap = os + RS * LS_GROUP * cols;       // [DMAX]: launch A, the product of the block's decays
+  float* bs = ap + DMAX;                       // [GROUP]: the bonus number of each token
+  const bool col = c < vdim;
+  float* sp = a.mode == 0 ? a.state + (((size_t)a.state_slots[r] * a.heads + h) * dim) * vdim + c
+                          : a.z + (((size_t)blockIdx.y * a.heads + h) * dim) * vdim + c;
+  if (a.mode == 1) for (int i = threadIdx.x; i < DMAX; i += blockDim.x) ap[i] = 1.f;
+  float S[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) S[i] = (a.mode != 1 && col && r0 + i < dim) ? sp[(size_t)(r0 + i) * vdim] : 0.f;
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float head_decay = a.decay ? a.decay[h] : 1.f;
+  for (int g0 = t0; g0 < t1; g0 += LS_GROUP) {
+    const int cnt = min(LS_GROUP, t1 - g0);
+    for (int idx = threadIdx.x; idx < cnt * DMAX; idx += blockDim.x) {
+      const int t = idx / DMAX, i = idx % DMAX;
+      float qv = 0.f, kv = 0.f, dv = 1.f;
+      if (i < dim) {
+        const size_t tok = (size_t)(g0 + t);
+        qv = a.q[tok * a.ldq + h * dim + i];
+        kv = a.k[tok * a.ldk + h * dim + i] * a.key_scale;
+        dv = a.decay ? head_decay
+                     : expf(-expf(a.w[tok * a.ldw + h * dim + i] + load_as_f32(a.w_bias, a.p_dtype, (size_t)h * dim + i)));
+      }
+      qs[idx] = qv;
+      ks[idx] = kv;
+      ds[idx] = dv;
+    }
+    for (int idx = threadIdx.x; idx < cnt * width; idx += blockDim.x) {
+      const int t = idx / width, e = idx % width;
+      vs[t * cols + e] = a.v[(size_t)(g0 + t) * a.ldv + h * vdim + c0 + e];
+    }
+    __syncthreads();
+    if (BONUS)                                   // b_t = sum_i u[i] k[i] q[i], a warp per token
+      for (int t = warp; t < cnt; t += warps) {
+        float b = 0.f;
+        for (int i = lane; i < dim; i += 32)
+          b += load_as_f32(a.bonus, a.p_dtype, (size_t)h * dim + i) * ks[t * DMAX + i] * qs[t * DMAX + i];
+        b = warp_sum(b);
+        if (lane == 0) bs[t] = b;
+      }
+    if (a.mode == 1)                            // each row's decays of this group into the block's product (a row has one owner)
+      for (int i = threadIdx.x; i < DMAX; i += blockDim.x) {
+        float pr = ap[i];
+        for (int t = 0; t < cnt; ++t) pr *= ds[t * DMAX + i];
+        ap[i] = pr;
+      }
+    if (BONUS) __syncthreads();
+    if (col) {
+      for (int t = 0; t < cnt; ++t) {
+        const float v = vs[t * cols + cid];
+        const float4* q4 = reinterpret_cast<const float4*>(qs + t * DMAX + r0);
+        const float4* k4 = reinterpret_cast<const float4*>(ks + t * DMAX + r0);
+        const float4* d4 = reinterpret_cast<const float4*>(ds + t * DMAX + r0);
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPT / 4; ++i) {
+          const float4 di = d4[i], ki = k4[i];
+          if (OUT && BONUS) {                   // the output reads the state before this token's update
+            const float4 qi = q4[i];
+            o0 = fmaf(S[4 * i], qi.x, o0); o1 = fmaf(S[4 * i + 1], qi.y, o1);
+            o2 = fmaf(S[4 * i + 2], qi.z, o2); o3 = fmaf(S[4 * i + 3], qi.w, o3);
+          }
+          S[4 * i] = fmaf(di.x, S[4 * i], ki.x * v);
+          S[4 * i + 1] = fmaf(di.y, S[4 * i + 1], ki.y * v);
+          S[4 * i + 2] = fmaf(di.z, S[4 * i + 2], ki.z * v);
+          S[4 * i + 3] = fmaf(di.w, S[4 * i + 3], ki.w * v);
+          if (OUT && !BONUS) {
+            const float4 qi = q4[i];
+            o0 = fmaf(S[4 * i], qi.x, o0); o1 = fmaf(S[4 * i + 1], qi.y, o1);
+            o2 = fmaf(S[4 * i + 2], qi.z, o2); o3 = fmaf(S[4 * i + 3], qi.w, o3);
+          }
+        }
+        float o = (o0 + o1) + (o2 + o3);
+        if (OUT && BONUS && part == 0) o = fmaf(v, bs[t], o);
+        os[(part * LS_GROUP + t) * cols + cid] = o;
+      }
+    }
+    __syncthreads();
+    for (int t = warp; t < cnt && a.mode != 1; t += warps) {           // the head's finish, a warp per token
+      const float* o = os + t * cols;
+      if (a.raw) {                                      // the head has other slabs: the second kernel finishes it
+        float* dst = a.raw + ((size_t)(g0 + t) * a.heads + h) * vdim + c0;
+        for (int e = lane; e < width; e += 32) {
+          float v = o[e];
+          for (int p = 1; p < RS; ++p) v += o[p * LS_GROUP * cols + e];
+          dst[e] = v;
+        }
+        continue;
+      }
+      ls_finish<T>(a, o, g0 + t, h, lane, RS, LS_GROUP * cols);
+    }
+    __syncthreads();
+  }
+  if (col && a.mode != 2) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i)
+      if (r0 + i < dim) sp[(size_t)(r0 + i) * vdim] = S[i];
+  }
+  if (a.mode == 1 && c0 == 0)
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) a.dprod[((size_t)blockIdx.y * a.heads + h) * dim + i] = ap[i];
+}
+
 // Launch B: a thread per element (head, row, column) of a request's state carries it over the request's blocks.
 __global__ void __launch_bounds__(256)
 linear_scan_carry_kernel(LinearScanArgs a) {
@@ -306,6 +443,12 @@ static int ls_block_threads(int dim, int vdim) {
   return min(cap, ((vdim + 31) / 32) * 32);
 }
 
+// The rows of a column over two threads where the block then still fits (heads of more than 32 rows)
+static int ls_row_split(int dim, int vdim) {
+  const int cap = ls_max_threads(dim <= 16 ? 16 : dim <= 32 ? 32 : dim <= 64 ? 64 : 128);
+  return (dim > 32 && 2 * ls_block_threads(dim, vdim) <= cap) ? 2 : 1;
+}
+
 template <typename T, bool BONUS>
 static int ls_launch(LinearScanArgs a, int requests, int tokens, cudaStream_t s) {
   if (a.dim > 128) {
@@ -314,7 +457,8 @@ static int ls_launch(LinearScanArgs a, int requests, int tokens, cudaStream_t s)
     IFB_ALLOW_SMEM(linear_scan_wide_kernel<T>, wide);
     return ifb_launch(linear_scan_wide_kernel<T>, dim3(a.heads, requests), dim3(256), wide, s, a);
   }
-  const int threads = ls_block_threads(a.dim, a.vdim);
+  const int threads = ls_block_threads(a.dim, a.vdim);          // threads along the columns
+  const bool split = ls_row_split(a.dim, a.vdim) == 2;
   a.slabs = (a.vdim + threads - 1) / threads;
   if (a.slabs > 1 && !a.raw) return IFB_ERR_ARG;
   if (a.slabs == 1) a.raw = nullptr;
@@ -322,7 +466,7 @@ static int ls_launch(LinearScanArgs a, int requests, int tokens, cudaStream_t s)
   int st = IFB_ERR_SIZE;
   bool done = false;
 #define LS_CASE(D)                                                                              \
-  if (!done && a.dim <= D) {                                                                    \
+  if (!done && a.dim <= D && !(split && D >= 64)) {                                             \
     const size_t smem = ((size_t)LS_GROUP * (3 * D + 2 * threads) + D + LS_GROUP) * sizeof(float); \
     done = true;                                                                                \
     if (a.mode == 1) {                                                                          \
@@ -333,8 +477,21 @@ static int ls_launch(LinearScanArgs a, int requests, int tokens, cudaStream_t s)
       st = ifb_launch(linear_scan_kernel<T, D, true, BONUS>, grid, dim3(threads), smem, s, a);  \
     }                                                                                           \
   }
-  LS_CASE(16) LS_CASE(32) LS_CASE(64) LS_CASE(128)
+#define LS_SPLIT(D)                                                                                       \
+  if (!done && a.dim <= D && split) {                                                                     \
+    const size_t smem = ((size_t)LS_GROUP * (3 * D + 3 * threads) + D + LS_GROUP) * sizeof(float);        \
+    done = true;                                                                                          \
+    if (a.mode == 1) {                                                                                    \
+      IFB_ALLOW_SMEM((linear_scan_split_kernel<T, D, 2, false, BONUS>), smem);                            \
+      st = ifb_launch(linear_scan_split_kernel<T, D, 2, false, BONUS>, grid, dim3(2 * threads), smem, s, a); \
+    } else {                                                                                              \
+      IFB_ALLOW_SMEM((linear_scan_split_kernel<T, D, 2, true, BONUS>), smem);                             \
+      st = ifb_launch(linear_scan_split_kernel<T, D, 2, true, BONUS>, grid, dim3(2 * threads), smem, s, a);  \
+    }                                                                                                     \
+  }
+  LS_CASE(16) LS_CASE(32) LS_SPLIT(64) LS_CASE(64) LS_SPLIT(128) LS_CASE(128)
 #undef LS_CASE
+#undef LS_SPLIT
   if (st != IFB_OK || a.slabs == 1 || a.mode == 1) return st;
   const long long items = (long long)tokens * a.heads;
   return ifb_launch(linear_scan_finish_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, a, items);

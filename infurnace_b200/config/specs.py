@@ -404,9 +404,13 @@ class NormedEmbeddingSpec:
     weight: str
     norm: object
     keep: bool = False
+    unused: Tuple[str, ...] = ()          # tables [rows, width] a folder may hold although no part reads them
 
     def tensors(self) -> Mapping[str, TensorSpec]:
-        return {self.weight: TensorSpec((self.vocab_size, self.hidden_size)), **self.norm.tensors()}
+        t = {self.weight: TensorSpec((self.vocab_size, self.hidden_size)), **self.norm.tensors()}
+        for name in self.unused:
+            t[name] = TensorSpec((None, self.hidden_size), optional=True)
+        return t
 
 
 @dataclass(frozen=True)

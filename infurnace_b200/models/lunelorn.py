@@ -90,7 +90,9 @@ def build_lunelorn_plan(cfg: LunelornConfig) -> ModelPlan:
         vocab_size=V,
         hidden_size=W,
         max_positions=MAX_POSITIONS,
-        embedding=NormedEmbeddingSpec(V, W, "embed", RMSNormSpec(W, eps, "embed.norm"), keep=times > 1),
+        # a loop over an empty range runs nothing; its per-pass table may still be stored
+        embedding=NormedEmbeddingSpec(V, W, "embed", RMSNormSpec(W, eps, "embed.norm"), keep=times > 1,
+                                      unused=("loop.step",) if loop is not None and not looped else ()),
         layers=tuple(layers),
         schedule=tuple(schedule),
         final_norm=RMSNormSpec(W, eps, "final.norm"),
